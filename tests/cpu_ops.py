@@ -21,13 +21,16 @@ def install(monkeypatch):
         monkeypatch.setattr(ops, name, globals()[name])
 
 
-def embedding(ids, table, out):
+def embedding(ids, table, out, scale=1.0):
     idx = ids.long()
-    out.copy_(torch.where((idx >= 0)[:, None], table[idx.clamp(min=0)].float(), torch.zeros(())))
+    out.copy_(torch.where((idx >= 0)[:, None], table[idx.clamp(min=0)].float() * scale, torch.zeros(())))
     return out
 
 
-def add_rmsnorm(h, delta, gain, eps, out, rows=None):
+def add_rmsnorm(h, delta, gain, eps, out, rows=None, post_gain=None, post_eps=0.0):
+    if post_gain is not None:
+        d = delta.float()
+        delta = post_gain.float() * d * torch.rsqrt((d * d).mean(-1, keepdim=True) + post_eps)
     v = h if delta is None else h + delta.float()
     if rows is None:
         if delta is not None:
@@ -39,14 +42,20 @@ def add_rmsnorm(h, delta, gain, eps, out, rows=None):
     return out
 
 
-def swiglu(gate_up, out, interleaved=False):
+def _act(g, act):
+    if act == "gelu_tanh":
+        return 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    return g / (1 + torch.exp(-g))
+
+
+def swiglu(gate_up, out, interleaved=False, act="silu"):
     inter = out.shape[1]
     if interleaved:                  # groups of sixteen columns: eight gates, their eight ups
         pairs = gate_up.float().reshape(gate_up.shape[0], inter // 8, 2, 8)
         g, u = pairs[:, :, 0].reshape(-1, inter), pairs[:, :, 1].reshape(-1, inter)
     else:
         g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
-    out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+    out.copy_((_act(g, act) * u).to(out.dtype))
     return out
 
 
@@ -68,10 +77,10 @@ def interleave_gate_up(gate, up):
     return torch.stack([gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
 
 
-def linear_swiglu(x, w_gate_up, out_dtype, interleaved=False):
+def linear_swiglu(x, w_gate_up, out_dtype, interleaved=False, act="silu"):
     gate_up = linear(x, w_gate_up, out_dtype)
     out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=out_dtype)
-    return swiglu(gate_up, out, interleaved)
+    return swiglu(gate_up, out, interleaved, act)
 
 
 def qk_norm_rope_store(qkv, q_gain, k_gain, eps, inv_freq, rotary_dim, positions, token_slot,

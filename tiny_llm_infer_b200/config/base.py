@@ -80,13 +80,15 @@ def architecture_of(raw: Dict[str, Any]) -> str:
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         return str(archs[0])
+    if isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]          # designs that name themselves with one string
     model_type = raw.get("model_type")
     if model_type is not None:
         for name, entry in _ARCHITECTURES.items():
             if model_type in entry.model_types:
                 return name
     raise ConfigError(
-        "config.json names no architecture: 'architectures' is missing or empty and "
+        "config.json names no architecture: 'architectures' and 'architecture' are missing or empty and "
         f"model_type={model_type!r} is not registered; registered: {known_architectures()}")
 
 

@@ -22,6 +22,15 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// Activation of the gate in a gated feed-forward unit, act(gate) * up, by code.
+enum GateAct : int { kActSilu = 0, kActGeluTanh = 1 };
+
+__device__ __forceinline__ float gate_act(float g, int act) {
+    if (act == kActGeluTanh)   // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+        return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -71,12 +71,12 @@ template <> struct Vec8<bf16> {
 };
 
 // ---------------------------------------------------------------- embedding
-// out[t, :] = table[ids[t], :] widened to float32.  Rows with ids[t] < 0 (padding of a
+// out[t, :] = table[ids[t], :] * scale, widened to float32 before the product (scale 1 for a plain look-up).  Rows with ids[t] < 0 (padding of a
 // fixed-size batch) become zero.  Ids are range-checked on the host; the clamp below
 // only keeps a faulty caller from reading outside the table.
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, float scale) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -87,12 +87,12 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restri
     }
     if (id >= vocab) id = vocab - 1;
     const TW* src = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<TW>(src[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<TW>(src[i]) * scale;
 }
 
 template <typename TW>
 __global__ void embedding_vec_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                     float* __restrict__ out, int hidden, int vocab) {
+                                     float* __restrict__ out, int hidden, int vocab, float scale) {
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -103,6 +103,8 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const TW* __re
     for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (!pad) Vec8<TW>::load(src + c * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] *= scale;
         Vec8<float>::store(dst + c * 8, v);
     }
 }
@@ -202,12 +204,115 @@ __global__ void add_rmsnorm_vec_kernel(float* h, const TD* delta,
     }
 }
 
+// ---------------------------------------------------------------- norm of a sub-layer's output + add + RMSNorm
+// For blocks that norm a sub-layer's output before the residual sum ("sandwich" norms):
+// d' = post_gain * d / sqrt(mean(d^2) + post_eps);  v = h[r, :] + d';  out[o, :] = gain * v / sqrt(mean(v^2) + eps).
+// Rows and write-back as in add_rmsnorm; d' never leaves the registers, so the residual sum takes the
+// normed output in float32 whatever the storage type.
+template <typename TD, typename TG, typename TO>
+__global__ void postnorm_add_rmsnorm_kernel(float* h, const TD* delta, const TG* __restrict__ post_gain,
+                                            float post_eps, const TG* __restrict__ gain, float eps,
+                                            TO* __restrict__ out, const int* __restrict__ rows, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    TO* dst = out + (size_t)o * width;
+    if (r < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<TO>(0.0f);
+        return;
+    }
+    float* hr = h + (size_t)r * width;
+    const TD* dr = delta + (size_t)r * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = to_f32<TD>(dr[i]);
+        sum += d * d;
+    }
+    sum = block_sum(sum, scratch);
+    const float post_scale = 1.0f / sqrtf(sum / (float)width + post_eps);
+    float sum2 = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = hr[i] + to_f32<TD>(dr[i]) * post_scale * to_f32<TG>(post_gain[i]);
+        sum2 += v * v;
+    }
+    sum2 = block_sum(sum2, scratch);
+    const float scale = 1.0f / sqrtf(sum2 / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = hr[i] + to_f32<TD>(dr[i]) * post_scale * to_f32<TG>(post_gain[i]);
+        if (rows == nullptr) hr[i] = v;
+        dst[i] = from_f32<TO>(v * scale * to_f32<TG>(gain[i]));
+    }
+}
+
+template <typename TD, typename TG, typename TO, int CHUNKS>
+__global__ void postnorm_add_rmsnorm_vec_kernel(float* h, const TD* delta, const TG* __restrict__ post_gain,
+                                                float post_eps, const TG* __restrict__ gain, float eps,
+                                                TO* __restrict__ out, const int* __restrict__ rows, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    TO* dst = out + (size_t)o * width;
+    const int n_chunks = width >> 3;
+    if (r < 0) {
+        const float zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) Vec8<TO>::store(dst + c * 8, zero);
+        return;
+    }
+    float* hr = h + (size_t)r * width;
+    const TD* dr = delta + (size_t)r * width;
+    float v[CHUNKS][8], d[CHUNKS][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<float>::load(hr + c * 8, v[j]);
+            Vec8<TD>::load(dr + c * 8, d[j]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sum += d[j][e] * d[j][e];
+        }
+    }
+    sum = block_sum(sum, scratch);
+    const float post_scale = 1.0f / sqrtf(sum / (float)width + post_eps);
+    float sum2 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float g[8];
+            Vec8<TG>::load(post_gain + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[j][e] += d[j][e] * post_scale * g[e];
+                sum2 += v[j][e] * v[j][e];
+            }
+            if (rows == nullptr) Vec8<float>::store(hr + c * 8, v[j]);
+        }
+    }
+    sum2 = block_sum(sum2, scratch);
+    const float scale = 1.0f / sqrtf(sum2 / (float)width + eps);
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            float g[8];
+            Vec8<TG>::load(gain + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g[e] = v[j][e] * scale * g[e];
+            Vec8<TO>::store(dst + c * 8, g);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gate) * up, silu(x) = x / (1 + exp(-x)), in float32.  Stacked columns: gate at
+// out[t, i] = act(gate) * up in float32; act is silu(x) = x / (1 + exp(-x)) or the tanh form of
+// GELU (`gate_act` in common.cuh).  Stacked columns: gate at
 // gu[t, i], up at gu[t, inter + i].  Interleaved by eight: columns come in groups of sixteen,
 // eight gates followed by their eight ups, so gate at gu[t, 16 (i / 8) + i % 8] and up 8 further.
 template <typename T>
-__global__ void swiglu_kernel(const T* gu, T* out, int inter, int interleaved,
+__global__ void swiglu_kernel(const T* gu, T* out, int inter, int interleaved, int act,
                               size_t total) {
     TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -217,12 +322,12 @@ __global__ void swiglu_kernel(const T* gu, T* out, int inter, int interleaved,
         const size_t gi = interleaved ? 16 * (i >> 3) + (i & 7) : i, ui = interleaved ? gi + 8 : inter + i;
         const float g = to_f32<T>(gu[t * 2 * inter + gi]);
         const float u = to_f32<T>(gu[t * 2 * inter + ui]);
-        out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+        out[idx] = from_f32<T>(gate_act(g, act) * u);
     }
 }
 
 template <typename T>
-__global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleaved,
+__global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleaved, int act,
                                   size_t total_chunks) {
     TLLM_PDL_ENTER();
     const int per_row = inter >> 3;
@@ -234,7 +339,7 @@ __global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleave
         Vec8<T>::load(gu + t * 2 * inter + (interleaved ? c * 16 : c * 8), g);
         Vec8<T>::load(gu + t * 2 * inter + (interleaved ? c * 16 + 8 : inter + c * 8), u);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+        for (int e = 0; e < 8; ++e) g[e] = gate_act(g[e], act) * u[e];
         Vec8<T>::store(out + t * inter + c * 8, g);
     }
 }
@@ -292,6 +397,32 @@ static int launch_add_rmsnorm(float* h, const void* delta, const void* gain, int
     return launch_add_rmsnorm_typed<TD, float, TO>(h, delta, gain, eps, out, rows, n_out, width, stream);
 }
 
+template <typename TD, typename TG, typename TO>
+static int launch_postnorm_typed(float* h, const void* delta, const void* post_gain, float post_eps,
+                                 const void* gain, float eps, void* out, const int* rows, int n_out,
+                                 int width, cudaStream_t stream) {
+    const bool vec = width % 8 == 0 && aligned16(h) && aligned16(delta) && aligned16(gain) &&
+                     aligned16(post_gain) && aligned16(out);
+    const int chunks = width / 8;
+    if (vec && chunks <= 1024 * 4) {
+        int block = 64;
+        while (block < 1024 && block < chunks) block *= 2;
+        const int per_thread = (chunks + block - 1) / block;
+#define VEC_LAUNCH(C)                                                                                        \
+    launch_pdl(kPdlNorm, postnorm_add_rmsnorm_vec_kernel<TD, TG, TO, C>, dim3(n_out), dim3(block), 0, stream, \
+               h, (const TD*)delta, (const TG*)post_gain, post_eps, (const TG*)gain, eps, (TO*)out, rows, width)
+        if (per_thread <= 1) VEC_LAUNCH(1);
+        else if (per_thread <= 2) VEC_LAUNCH(2);
+        else VEC_LAUNCH(4);
+#undef VEC_LAUNCH
+    } else {
+        const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        launch_pdl(kPdlNorm, postnorm_add_rmsnorm_kernel<TD, TG, TO>, dim3(n_out), dim3(block), 0, stream,
+                   h, (const TD*)delta, (const TG*)post_gain, post_eps, (const TG*)gain, eps, (TO*)out, rows, width);
+    }
+    return finish_launch("postnorm_add_rmsnorm");
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -301,18 +432,18 @@ extern "C" {
 const char* tllm_last_error() { return g_error; }
 
 int tllm_embedding(const int* ids, const void* table, int table_dtype, float* out, int tokens,
-                   int hidden, int vocab, cudaStream_t stream) {
+                   int hidden, int vocab, float scale, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
     TLLM_REQUIRE(table_dtype == kBF16 || table_dtype == kF32, "embedding: unknown dtype %d", table_dtype);
     if (tokens == 0) return 0;
     const bool vec = hidden % 8 == 0 && aligned16(table) && aligned16(out);
     const int block = vec ? (hidden >= 2048 ? 256 : 128) : (hidden >= 1024 ? 256 : 128);
     if (table_dtype == kBF16) {
-        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
-        else launch_pdl(kPdlOther, embedding_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab);
+        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale);
+        else launch_pdl(kPdlOther, embedding_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale);
     } else {
-        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
-        else launch_pdl(kPdlOther, embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab);
+        if (vec) launch_pdl(kPdlOther, embedding_vec_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab, scale);
+        else launch_pdl(kPdlOther, embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab, scale);
     }
     return finish_launch("embedding");
 }
@@ -332,8 +463,26 @@ int tllm_add_rmsnorm(float* h, const void* delta, const void* gain, int gain_dty
     TLLM_REQUIRE(false, "add_rmsnorm: unknown dtype %d", act_dtype);
 }
 
+// As tllm_add_rmsnorm with `delta` normed (gain `post_gain`, `post_eps`) before it is added.  Both
+// gains have the storage type `gain_dtype`.
+int tllm_postnorm_add_rmsnorm(float* h, const void* delta, const void* post_gain, float post_eps,
+                              const void* gain, int gain_dtype, float eps, void* out, int act_dtype,
+                              const int* rows, int n_out, int width, cudaStream_t stream) {
+    TLLM_REQUIRE(n_out >= 0 && width > 0, "postnorm_add_rmsnorm: bad sizes");
+    TLLM_REQUIRE(delta != nullptr && post_gain != nullptr && gain != nullptr, "postnorm_add_rmsnorm: missing operand");
+    TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "postnorm_add_rmsnorm: unknown gain dtype");
+    TLLM_REQUIRE(eps > 0.0f && post_eps > 0.0f, "postnorm_add_rmsnorm: eps must be positive");
+    if (n_out == 0) return 0;
+#define POSTNORM(TD, TG, TO) launch_postnorm_typed<TD, TG, TO>(h, delta, post_gain, post_eps, gain, eps, out, rows, n_out, width, stream)
+    if (act_dtype == kBF16) return gain_dtype == kBF16 ? POSTNORM(bf16, bf16, bf16) : POSTNORM(bf16, float, bf16);
+    if (act_dtype == kF32) return gain_dtype == kBF16 ? POSTNORM(float, bf16, float) : POSTNORM(float, float, float);
+#undef POSTNORM
+    TLLM_REQUIRE(false, "postnorm_add_rmsnorm: unknown dtype %d", act_dtype);
+}
+
 int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter, int interleaved,
-                cudaStream_t stream) {
+                int act, cudaStream_t stream) {
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "swiglu: unknown activation %d", act);
     TLLM_REQUIRE(tokens >= 0 && inter > 0, "swiglu: bad sizes");
     TLLM_REQUIRE(!interleaved || inter % 8 == 0, "swiglu: interleaved columns need a multiple of 8, not %d", inter);
     TLLM_REQUIRE(dtype == kBF16 || dtype == kF32, "swiglu: unknown dtype %d", dtype);
@@ -344,15 +493,15 @@ int tllm_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter
         const size_t chunks = total / 8;
         const int grid = grid_for(chunks, block);
         if (dtype == kBF16)
-            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, act, chunks);
         else
-            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, chunks);
+            launch_pdl(kPdlSwiglu, swiglu_vec_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, act, chunks);
     } else {
         const int grid = grid_for(total, block);
         if (dtype == kBF16)
-            launch_pdl(kPdlSwiglu, swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)gate_up, (bf16*)out, inter, interleaved, act, total);
         else
-            launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, total);
+            launch_pdl(kPdlSwiglu, swiglu_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)gate_up, (float*)out, inter, interleaved, act, total);
     }
     return finish_launch("swiglu");
 }

@@ -61,9 +61,19 @@ def _declare(h) -> None:
     h.tllm_last_error.restype = ctypes.c_char_p
     h.tllm_last_error.argtypes = []
     sigs = {
-        "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, vp],
+        "tllm_embedding": [vp, vp, i32, vp, i32, i32, i32, f32, vp],
+        "tllm_postnorm_add_rmsnorm": [vp, vp, vp, f32, vp, i32, f32, vp, i32, vp, i32, i32, vp],
+        "tllm_qkv_unit_store": [vp, i32, vp, vp, f32, i32, vp, vp, vp, i32, i32, vp, vp, i64, vp, i32, i32,
+                                i32, i32, i32, i32, i32, vp],
+        "tllm_attention_biased_general": [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32,
+                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+        "tllm_moe_route": [vp, i32, i32, i32, i32, vp, vp, vp],
+        "tllm_moe_plan": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
+        "tllm_moe_grouped": [vp, i32, vp, vp, i32, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                             i32, i32, vp, vp],
+        "tllm_moe_combine": [vp, vp, vp, i32, vp, vp, i32, i32, i32, vp],
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
-        "tllm_swiglu": [vp, vp, i32, i32, i32, i32, vp],
+        "tllm_swiglu": [vp, vp, i32, i32, i32, i32, i32, vp],
         "tllm_cast": [vp, i32, vp, i32, i64, vp],
         "tllm_feed_tokens": [vp, vp, vp, vp, i32, vp],
         "tllm_qk_norm_rope_store": [vp, vp, vp, i32, f32, vp, i32, vp, vp, vp, i32, vp, i32, vp,
@@ -87,6 +97,8 @@ def _declare(h) -> None:
         fn = getattr(h, name)
         fn.argtypes = args
         fn.restype = i32
+    h.tllm_moe_tile_rows.argtypes = []
+    h.tllm_moe_tile_rows.restype = i32
     h.tllm_paged_attention_prefill_tc_rows.argtypes = [i32, i32]
     h.tllm_paged_attention_prefill_tc_rows.restype = i32
     h.tllm_sample_nucleus_scratch_bytes.argtypes = [i32]
@@ -134,25 +146,34 @@ def _dt(t: torch.Tensor) -> int:
 
 
 # --------------------------------------------------------------------------- ops
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[ids[t]] as float32; rows with a negative id become zero."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale as float32; rows with a negative id become zero."""
     _cuda(ids, table, out)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
     vocab, hidden = table.shape
     _check(lib().tllm_embedding(_p(ids), _p(table), _dt(table), _p(out), ids.numel(), hidden, vocab,
-                                _stream()), "embedding")
+                                float(scale), _stream()), "embedding")
     return out
 
 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                post_gain: Optional[torch.Tensor] = None, post_eps: float = 0.0) -> torch.Tensor:
     """h += delta (float32 sum, written back) and out = gain * h / sqrt(mean(h^2) + eps).
-    With ``rows`` only those rows are normed, into out[0..len(rows)), and h is not written."""
-    _cuda(h, delta, gain, out, rows)
+    With ``rows`` only those rows are normed, into out[0..len(rows)), and h is not written.
+    With ``post_gain`` the delta is normed itself before it is added:
+    h += post_gain * delta / sqrt(mean(delta^2) + post_eps), in float32 inside the same kernel."""
+    _cuda(h, delta, gain, out, rows, post_gain)
     assert h.dtype == torch.float32
     if delta is not None:
         assert delta.dtype == out.dtype and delta.shape == h.shape
     n_out = out.shape[0] if rows is None else rows.numel()
+    if post_gain is not None:
+        assert delta is not None and post_gain.dtype == gain.dtype
+        _check(lib().tllm_postnorm_add_rmsnorm(_p(h), _p(delta), _p(post_gain), float(post_eps), _p(gain), _dt(gain),
+                                               float(eps), _p(out), _dt(out), _p(rows), n_out, h.shape[-1], _stream()),
+               "postnorm_add_rmsnorm")
+        return out
     _check(lib().tllm_add_rmsnorm(_p(h), _p(delta), _p(gain), _dt(gain), float(eps), _p(out), _dt(out),
                                   _p(rows), n_out, h.shape[-1], _stream()), "add_rmsnorm")
     return out
@@ -168,14 +189,18 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
-    """out[t, i] = silu(gate) * up with gate = gate_up[t, i], up = gate_up[t, I + i], or, for columns
-    interleaved by eight, gate = gate_up[t, 16 (i // 8) + i % 8] and up eight columns further."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}      # codes of csrc/common.cuh (GateAct)
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False, act: str = "silu") -> torch.Tensor:
+    """out[t, i] = act(gate) * up with gate = gate_up[t, i], up = gate_up[t, I + i], or, for columns
+    interleaved by eight, gate = gate_up[t, 16 (i // 8) + i % 8] and up eight columns further.
+    ``act``: ``silu`` or ``gelu_tanh``."""
     _cuda(gate_up, out)
     tokens, two_i = gate_up.shape
     assert out.shape == (tokens, two_i // 2) and out.dtype == gate_up.dtype
-    _check(lib().tllm_swiglu(_p(gate_up), _p(out), _dt(out), tokens, two_i // 2, int(interleaved), _stream()),
-           "swiglu")
+    _check(lib().tllm_swiglu(_p(gate_up), _p(out), _dt(out), tokens, two_i // 2, int(interleaved),
+                             ACTIVATIONS[act], _stream()), "swiglu")
     return out
 
 
@@ -536,7 +561,7 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype,
-                  interleaved: bool = False) -> torch.Tensor:
+                  interleaved: bool = False, act: str = "silu") -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu], or with the rows of Wg and Wu
     interleaved by eight (``interleave_gate_up``).  With enough bfloat16 rows the product and the
     activation are one tcgen05 kernel, with few rows and interleaved weights one weight-streaming
@@ -544,11 +569,146 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dty
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
     plain = x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() \
-        and w_gate_up.is_contiguous()
+        and w_gate_up.is_contiguous() and act == "silu"
     if plain and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
         return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved)
     if plain and interleaved and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0:
         return gemm_skinny_swiglu(x, w_gate_up)
     gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
-    act = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
-    return swiglu(gate_up, act, interleaved)
+    out = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
+    return swiglu(gate_up, out, interleaved, act)
+
+
+# --------------------------------------------------------------------------- attention with a modified score
+def _plane(plane: torch.Tensor):
+    """(pointer, elements from one page to the next) of a cache plane [pages, heads, page, width]: a
+    view into the pages whose last three axes are dense."""
+    heads, page, width = plane.shape[1:]
+    assert plane.stride(3) == 1 and plane.stride(2) == width and plane.stride(1) == page * width
+    return plane.data_ptr(), plane.stride(0)
+
+
+def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slot, block_table,
+                   k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], page_size: int,
+                   q_heads: int, kv_heads: int, dk: int, dv: int, eps: Optional[float],
+                   q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
+                   store: bool = True) -> None:
+    """Rows of ``proj`` = q heads | k heads | v heads | anything: queries and keys divided per head by
+    their root mean square (``eps`` None: left as they are; gains optional), queries to ``q_out``,
+    keys and values of every row into their planes of the paged cache (``store``).  Keys have width
+    ``dk``, values ``dv``.  Rows with a negative slot are skipped."""
+    _cuda(proj, q_out, positions, token_slot, block_table, q_gain, k_gain)
+    assert q_out.dtype == proj.dtype and tuple(q_out.shape) == (proj.shape[0], q_heads * dk)
+    kp = vp = None
+    stride = 0
+    if store:
+        assert k_plane.dtype == v_plane.dtype == proj.dtype
+        assert tuple(k_plane.shape[1:]) == (kv_heads, page_size, dk) and tuple(v_plane.shape[1:]) == (kv_heads, page_size, dv)
+        (kp, stride), (vp, stride_v) = _plane(k_plane), _plane(v_plane)
+        assert stride == stride_v
+    _check(lib().tllm_qkv_unit_store(
+        _p(proj), proj.shape[1], _p(q_gain), _p(k_gain), float(eps or 1.0), int(eps is not None), _p(positions),
+        _p(token_slot), _p(block_table), block_table.shape[1] if block_table is not None else 0, page_size,
+        kp, vp, stride, _p(q_out), _dt(proj), proj.shape[0], q_heads, kv_heads, dk, dv, int(store), _stream()),
+        "qkv_unit_store")
+
+
+def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, positions, token_slot,
+                     block_table, page_size: int, q_heads: int, kv_heads: int, dk: int, dv: int, scale: float,
+                     out: torch.Tensor, softcap: float = 0.0, chunk: int = 0, window: int = 0,
+                     sink: bool = False, slopes: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None, ctx=None) -> torch.Tensor:
+    """Attention of every row of ``q`` [T, q_heads * dk] over the keys of its own request, with the
+    score s = (q . k) * scale changed in this order by whatever is given: ``softcap`` (s <- cap *
+    tanh(s / cap)), ``slopes`` [q_heads] float32 (s <- s - slope * (pos - key pos)); keys j <= pos from
+    the row's own ``chunk`` of positions and from its ``window``; ``sink``: one is added to the softmax's
+    denominator.  ``gate`` (a view [T, q_heads * dv] whose rows may be strided): out *= sigmoid(gate)."""
+    _cuda(q, positions, token_slot, block_table, out, slopes)
+    tokens = q.shape[0]
+    assert tuple(out.shape) == (tokens, q_heads * dv) and out.dtype == q.dtype
+    (kp, stride), (vp, stride_v) = _plane(k_plane), _plane(v_plane)
+    assert stride == stride_v and k_plane.dtype == q.dtype
+    gate_stride = 0
+    if gate is not None:
+        assert gate.dtype == q.dtype and gate.stride(1) == 1 and tuple(gate.shape) == tuple(out.shape)
+        gate_stride = gate.stride(0)
+    if slopes is not None:
+        assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
+    _check(lib().tllm_attention_biased_general(
+        _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(block_table), block_table.shape[1], page_size,
+        _dt(q), tokens, q_heads, kv_heads, dk, dv, float(scale), float(softcap or 0.0), int(chunk or 0),
+        int(window or 0), int(bool(sink)), _p(slopes), None if gate is None else gate.data_ptr(), gate_stride,
+        _p(out), _stream()), "attention_biased")
+    return out
+
+
+# --------------------------------------------------------------------------- mixture of experts
+def moe_tile_rows() -> int:
+    return int(lib().tllm_moe_tile_rows())
+
+
+def moe_route(z: torch.Tensor, top: int, softmax_weights: bool = False):
+    """(ids [T, top] int32, weights [T, top] float32) from float32 router logits ``z`` [T, E]: the
+    ``top`` experts with the largest logits; weight sigmoid(z), or softmax over the chosen ones."""
+    _cuda(z)
+    assert z.dtype == torch.float32
+    tokens, experts = z.shape
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=z.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=z.device)
+    _check(lib().tllm_moe_route(_p(z), tokens, experts, top, int(softmax_weights), _p(ids), _p(weights), _stream()),
+           "moe_route")
+    return ids, weights
+
+
+class MoePlan:
+    """Device-side lists that sort a step's (token, choice) assignments by expert."""
+
+    def __init__(self, ids: torch.Tensor, experts: int):
+        n = ids.numel()
+        self.n, self.experts = n, experts
+        self.max_tiles = n // moe_tile_rows() + experts
+        ints = torch.empty(experts + 2 + 3 * n + 2 * self.max_tiles, dtype=torch.int32, device=ids.device)
+        at = 0
+
+        def take(k):
+            nonlocal at
+            part = ints[at:at + k]
+            at += k
+            return part
+        self.offsets, self.n_tiles = take(experts + 1), take(1)
+        self.row_of, self.src_of, self.expert_of_row = take(n), take(n), take(n)
+        self.tile_expert, self.tile_row0 = take(self.max_tiles), take(self.max_tiles)
+        _check(lib().tllm_moe_plan(_p(ids), n, experts, _p(self.offsets), _p(self.n_tiles), _p(self.row_of),
+                                   _p(self.src_of), _p(self.expert_of_row), _p(self.tile_expert),
+                                   _p(self.tile_row0), _stream()), "moe_plan")
+
+
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, top: int, gated: bool, gather: bool,
+                weights: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
+    """Per row r of the plan, A[r] . W[expert of r]^T.  ``w`` is [E, N (or 2 N: gate rows, then up rows), K].
+    ``gather``: ``a`` is [tokens, K] and a row reads its token, times ``weights`` [tokens, top] if given.
+    ``gated``: the result is act(gate) * up [rows, N] in the storage type, else [rows, N] float32."""
+    _cuda(a, w, weights)
+    experts, n_total, k = w.shape
+    assert a.shape[1] == k and a.dtype == w.dtype and experts == plan.experts
+    n = n_total // 2 if gated else n_total
+    out = torch.empty((plan.n, n), dtype=a.dtype if gated else torch.float32, device=a.device)
+    _check(lib().tllm_moe_grouped(
+        _p(a), a.stride(0), _p(plan.src_of), _p(weights), top, _p(w), w.stride(0), _p(plan.tile_expert),
+        _p(plan.tile_row0), _p(plan.n_tiles), _p(plan.offsets), _p(plan.expert_of_row), plan.n, plan.max_tiles,
+        n, k, _dt(a), int(gated), int(gather), ACTIVATIONS[act], _p(out), _stream()), "moe_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, top: int, shared: Optional[torch.Tensor], dtype: torch.dtype,
+                weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = shared[t] + sum_k (weights[t, k] *) y[row of (t, k)], float32 sums, stored as ``dtype``."""
+    _cuda(y, shared, weights)
+    assert y.dtype == torch.float32
+    tokens, width = plan.n // top, y.shape[1]
+    out = torch.empty((tokens, width), dtype=dtype, device=y.device)
+    if shared is not None:
+        assert shared.dtype == dtype and tuple(shared.shape) == (tokens, width)
+    _check(lib().tllm_moe_combine(_p(y), _p(plan.row_of), _p(weights), top, _p(shared), _p(out), _DT[dtype],
+                                  tokens, width, _stream()), "moe_combine")
+    return out

@@ -4,6 +4,12 @@
 This is the reference's decoder layer (model/src/qwen3_paged_batch.cpp:146-301) with the
 two residual sums moved into the norm that follows them; the sum left over after the
 last layer is taken by the model's final norm.
+
+``sandwich``: a norm before and after each sub-layer, h += norm1b(mixer(norm1(h))), then
+h += norm2b(ffn(norm2(h))).  The output norms are not run on their own: the sub-layer's output goes
+on as a ``NormedDelta`` and the next norm kernel (this layer's norm2, the next layer's norm1, or
+the model's last norm) norms it, adds it and norms the sum.  ``sandwich_mixer`` is the same layer
+without a feed-forward.
 """
 from __future__ import annotations
 
@@ -43,3 +49,24 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, ctx, cache)
         x = self.norm2.forward(h, a)
         return self.ffn.forward(x, ctx)
+
+
+@register("block", "sandwich")
+class SandwichBlock(Block):
+    roles = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm",
+             "norm2": "norm", "ffn": "feed_forward", "norm2b": "norm"}
+
+    def forward(self, h: torch.Tensor, pending, ctx, cache):
+        x = self.norm1.forward(h, pending)
+        a = self.mixer.forward(x, ctx, cache)
+        x = self.norm2.forward(h, self.norm1b.wrap(a))
+        return self.norm2b.wrap(self.ffn.forward(x, ctx))
+
+
+@register("block", "sandwich_mixer")
+class SandwichMixerBlock(Block):
+    roles = {"norm1": "norm", "mixer": "mixer", "norm1b": "norm"}
+
+    def forward(self, h: torch.Tensor, pending, ctx, cache):
+        x = self.norm1.forward(h, pending)
+        return self.norm1b.wrap(self.mixer.forward(x, ctx, cache))

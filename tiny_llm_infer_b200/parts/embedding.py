@@ -1,6 +1,7 @@
 """Token embedding and the output head.
 
-h0[t] = E[token[t]], no scaling (reference: kernels/src/embed_kernel_cuda.cu:6-28); the
+h0[t] = E[token[t]] * scale, scale 1 unless the model gives one (reference, which has none:
+kernels/src/embed_kernel_cuda.cu:6-28); the
 logits of the wanted rows are hN[row] . W^T in float32.  The reference always uses the
 embedding matrix as W (model/src/qwen3_layers.cpp:246-265); here ``tied`` decides, and an
 untied head reads ``lm_head.weight``.
@@ -18,19 +19,23 @@ from .spec import ParamSpec
 
 @register("embedding", "token_embedding")
 class TokenEmbedding:
-    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device):
+    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device, scale: float = 1.0,
+                 name: str = "weight"):
         self.vocab, self.hidden, self.dtype, self.device = vocab_size, hidden_size, dtype, device
+        self.scale, self.name = float(scale), name
         self.weight: Optional[torch.Tensor] = None
 
     @classmethod
-    def param_specs(cls, vocab_size, hidden_size) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((vocab_size, hidden_size))}
+    def param_specs(cls, vocab_size, hidden_size, scale: float = 1.0, name: str = "weight") -> Dict[str, ParamSpec]:
+        return {name: ParamSpec((vocab_size, hidden_size))}
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
-        self.weight = t["weight"].contiguous()
+        self.weight = t[self.name].contiguous()
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         h = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
+        if self.scale != 1.0:
+            return ops.embedding(token_ids, self.weight, h, self.scale)
         return ops.embedding(token_ids, self.weight, h)
 
 

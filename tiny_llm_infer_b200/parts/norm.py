@@ -5,8 +5,14 @@ directly, no "1 + gain" (reference: kernels/src/rmsnorm_kernel_cuda.cu:17-38).  
 reference adds the residual in a separate half-precision kernel
 (model/src/qwen3_paged_batch.cpp:273-279); here the sum is float32 and happens in the
 same pass that computes the norm.
+
+A block that norms a sub-layer's output before the residual sum hands that output on as a
+``NormedDelta`` (``wrap``): the norm that follows takes it as its ``delta`` and does the output's norm,
+the sum and its own norm in one kernel, h += g_post * d / sqrt(mean(d^2) + eps_post) in float32.
 """
 from __future__ import annotations
+
+from dataclasses import dataclass
 
 from typing import Dict, Optional
 
@@ -17,21 +23,37 @@ from .registry import register
 from .spec import ParamSpec
 
 
+@dataclass
+class NormedDelta:
+    """A sub-layer's output that is to be normed (gain, eps) before it is added to the stream."""
+    delta: torch.Tensor
+    gain: torch.Tensor
+    eps: float
+
+
 @register("norm", "rmsnorm")
 class RMSNorm:
-    def __init__(self, width: int, eps: float, dtype: torch.dtype, device):
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device, name: str = "weight"):
         self.width, self.eps, self.dtype, self.device = int(width), float(eps), dtype, device
+        self.name = name
         self.gain: Optional[torch.Tensor] = None
 
     @classmethod
-    def param_specs(cls, width: int, eps: float) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((int(width),), "norm")}
+    def param_specs(cls, width: int, eps: float, name: str = "weight") -> Dict[str, ParamSpec]:
+        """``name``: what the gain is called behind the part's prefix in the checkpoint."""
+        return {name: ParamSpec((int(width),), "norm")}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.gain = tensors["weight"].contiguous()
+        self.gain = tensors[self.name].contiguous()
 
-    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor],
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def wrap(self, delta: torch.Tensor) -> NormedDelta:
+        """``delta`` with this norm still to be applied to it, by the norm that adds it to the stream."""
+        return NormedDelta(delta, self.gain, self.eps)
+
+    def forward(self, h: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=self.dtype, device=h.device)
+        if isinstance(delta, NormedDelta):
+            post = delta.gain if delta.gain.dtype == self.gain.dtype else delta.gain.to(self.gain.dtype)
+            return ops.add_rmsnorm(h, delta.delta, self.gain, self.eps, out, rows, post_gain=post, post_eps=delta.eps)
         return ops.add_rmsnorm(h, delta, self.gain, self.eps, out, rows)
