@@ -214,6 +214,385 @@ static int launch_general(const void* q, const void* kp, const void* vp, long lo
     return finish_launch("attention_biased_general");
 }
 
+// ---------------------------------------------------------------- prompt portions, bfloat16, mma.sync
+// A block owns 64 consecutive query rows of one portion and one query head and walks the keys its rows
+// can see in tiles of 64 (flash-attention style: S and the softmax in float32 registers, P V accumulated
+// in float32).  Keys and values are staged by cp.async in two buffers; a row of a tile is padded by 16
+// bytes so that ldmatrix meets no bank conflict, and widths below DKP / DVP are filled with zeros.
+constexpr int kPfWarps = 4, kPfM = 64, kPfN = 64, kPfPad = 8;
+
+template <int DKP, int DVP>
+__global__ void __launch_bounds__(kPfWarps * 32)
+attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
+                                const int* __restrict__ seg_info, const int* __restrict__ tiles,
+                                const int* __restrict__ block_table, int max_pages, int page_size,
+                                int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
+                                const float* __restrict__ slopes, const bf16* gate, int gate_stride,
+                                bf16* __restrict__ out) {
+    extern __shared__ __align__(128) unsigned char pf_smem[];
+    TLLM_PDL_ENTER();
+    constexpr int kKRow = DKP + kPfPad, kVRow = DVP + kPfPad;           // elements per padded row
+    constexpr int kKBytes = kPfN * kKRow * 2, kVBytes = kPfN * kVRow * 2;
+    const int seg = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
+    const int head = blockIdx.y;
+    const int slot = seg_info[4 * seg], start = seg_info[4 * seg + 1];
+    const int len = seg_info[4 * seg + 2], pos0 = seg_info[4 * seg + 3];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = head / (q_heads / kv_heads);
+    const int* table = block_table + (size_t)slot * max_pages;
+    const float slope = slopes != nullptr ? slopes[head] : 0.0f;
+
+    const int rows_here = min(kPfM, len - q_off);
+    const int first_pos = pos0 + q_off, last_pos = first_pos + rows_here - 1;
+    const int lo_all = first_key(first_pos, mod);
+    const int kt_first = lo_all / kPfN, kt_last = last_pos / kPfN;
+
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const bool v_lo = r_lo < rows_here, v_hi = r_hi < rows_here;
+    const int p_lo = first_pos + r_lo, p_hi = first_pos + r_hi;
+    const int f_lo = first_key(p_lo, mod), f_hi = first_key(p_hi, mod);
+    const bf16* q_lo = q + ((size_t)(start + q_off + r_lo) * q_heads + head) * dk;
+    const bf16* q_hi = q + ((size_t)(start + q_off + r_hi) * q_heads + head) * dk;
+    uint32_t qa[DKP / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < DKP / 16; ++ks) {
+        const int c0 = ks * 16 + (lane & 3) * 2;
+        qa[ks][0] = (v_lo && c0 < dk) ? *reinterpret_cast<const uint32_t*>(q_lo + c0) : 0u;
+        qa[ks][1] = (v_hi && c0 < dk) ? *reinterpret_cast<const uint32_t*>(q_hi + c0) : 0u;
+        qa[ks][2] = (v_lo && c0 + 8 < dk) ? *reinterpret_cast<const uint32_t*>(q_lo + c0 + 8) : 0u;
+        qa[ks][3] = (v_hi && c0 + 8 < dk) ? *reinterpret_cast<const uint32_t*>(q_hi + c0 + 8) : 0u;
+    }
+    const int w_first = first_pos + warp * 16;
+    const int w_last = min(w_first + 15, last_pos);
+    const int w_lo = first_key(w_first, mod);
+
+    float o[DVP / 8][4];
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    // the sink: a key of score 0 without a value, counted once per row (by the first lane of its four)
+    float m_lo = mod.sink ? 0.0f : -INFINITY, m_hi = m_lo;
+    float l_lo = (mod.sink && (lane & 3) == 0) ? 1.0f : 0.0f, l_hi = l_lo;
+
+    auto issue = [&](int kt, int stage) {
+        const uint32_t ks = smem_u32(pf_smem + (size_t)stage * (kKBytes + kVBytes));
+        const uint32_t vs = ks + kKBytes;
+        constexpr int kKC = DKP / 8, kVC = DVP / 8;
+        for (int c = threadIdx.x; c < kPfN * kKC; c += kPfWarps * 32) {
+            const int row = c / kKC, chunk = c % kKC;
+            const int key = kt * kPfN + row;
+            const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
+            const bool ok = page >= 0 && chunk * 8 < dk;
+            const bf16* src = k_plane + (ok ? (long long)page * page_stride + ((size_t)g * page_size + key % page_size) * dk + chunk * 8 : 0);
+            cp_async_16(ks + (row * kKRow + chunk * 8) * 2, src, ok);
+        }
+        for (int c = threadIdx.x; c < kPfN * kVC; c += kPfWarps * 32) {
+            const int row = c / kVC, chunk = c % kVC;
+            const int key = kt * kPfN + row;
+            const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
+            const bool ok = page >= 0 && chunk * 8 < dv;
+            const bf16* src = v_plane + (ok ? (long long)page * page_stride + ((size_t)g * page_size + key % page_size) * dv + chunk * 8 : 0);
+            cp_async_16(vs + (row * kVRow + chunk * 8) * 2, src, ok);
+        }
+        cp_async_commit();
+    };
+
+    const int k_steps = (dk + 15) / 16, v_pairs = (dv + 15) / 16;
+    issue(kt_first, 0);
+    for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int stage = (kt - kt_first) & 1;
+        if (kt + 1 <= kt_last) {
+            issue(kt + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int key0 = kt * kPfN;
+        const bool active = warp * 16 < rows_here && key0 <= w_last && key0 + kPfN - 1 >= w_lo;
+        if (active) {
+            const uint32_t ks_base = smem_u32(pf_smem + (size_t)stage * (kKBytes + kVBytes));
+            const uint32_t vs_base = ks_base + kKBytes;
+            const int mid = lane >> 3, mrow = lane & 7;
+            float s[kPfN / 8][4];
+#pragma unroll
+            for (int i = 0; i < kPfN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < DKP / 16; ++ks) {
+                if (ks < k_steps) {
+#pragma unroll
+                    for (int nt2 = 0; nt2 < kPfN / 16; ++nt2) {
+                        uint32_t kb[4];
+                        ldmatrix_x4(kb, ks_base + ((nt2 * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
+                        const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+                        mma_bf16_16816(s[2 * nt2], qa[ks], b0);
+                        mma_bf16_16816(s[2 * nt2 + 1], qa[ks], b1);
+                    }
+                }
+            }
+            const int key_base = key0 + (lane & 3) * 2;
+            float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < kPfN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = key_base + nt * 8 + e;
+                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score(s[nt][e], slope, p_lo - j, mod) : -INFINITY;
+                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score(s[nt][2 + e], slope, p_hi - j, mod) : -INFINITY;
+                    tmax_lo = fmaxf(tmax_lo, s[nt][e]);
+                    tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
+                }
+            tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
+            tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
+            tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
+            tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
+            const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
+            const float ms_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
+            const float c_lo = expf(m_lo - ms_lo), c_hi = expf(m_hi - ms_hi);
+            m_lo = mn_lo;
+            m_hi = mn_hi;
+            float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < kPfN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    s[nt][e] = expf(s[nt][e] - ms_lo);
+                    s[nt][2 + e] = expf(s[nt][2 + e] - ms_hi);
+                    sum_lo += s[nt][e];
+                    sum_hi += s[nt][2 + e];
+                }
+            l_lo = l_lo * c_lo + sum_lo;
+            l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < DVP / 8; ++i) {
+                o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+            }
+#pragma unroll
+            for (int kk = 0; kk < kPfN / 16; ++kk) {
+                const uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                        pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]),
+                                        pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                for (int c = 0; c < DVP / 8; c += 2) {
+                    if (c / 2 < v_pairs) {
+                        uint32_t vb[4];
+                        ldmatrix_x4_trans(vb, vs_base + ((kk * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
+                        const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+                        mma_bf16_16816(o[c], pa, b0);
+                        mma_bf16_16816(o[c + 1], pa, b1);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float inv_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, inv_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
+    const size_t row_lo = start + q_off + r_lo, row_hi = start + q_off + r_hi;
+    bf16* o_lo = out + (row_lo * q_heads + head) * dv;
+    bf16* o_hi = out + (row_hi * q_heads + head) * dv;
+    const bf16* g_lo = gate != nullptr ? gate + row_lo * gate_stride + (size_t)head * dv : nullptr;
+    const bf16* g_hi = gate != nullptr ? gate + row_hi * gate_stride + (size_t)head * dv : nullptr;
+#pragma unroll
+    for (int i = 0; i < DVP / 8; ++i) {
+        const int col = i * 8 + (lane & 3) * 2;
+        if (col >= dv) continue;
+        if (v_lo) {
+            float a = o[i][0] * inv_lo, b = o[i][1] * inv_lo;
+            if (g_lo != nullptr) {
+                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[col])));
+                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_lo[col + 1])));
+            }
+            *reinterpret_cast<uint32_t*>(o_lo + col) = pack_bf16(a, b);
+        }
+        if (v_hi) {
+            float a = o[i][2] * inv_hi, b = o[i][3] * inv_hi;
+            if (g_hi != nullptr) {
+                a *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[col])));
+                b *= 1.0f / (1.0f + expf(-__bfloat162float(g_hi[col + 1])));
+            }
+            *reinterpret_cast<uint32_t*>(o_hi + col) = pack_bf16(a, b);
+        }
+    }
+}
+
+template <int DKP, int DVP>
+static int launch_biased_prefill(const void* q, const void* kp, const void* vp, long long page_stride,
+                                 const int* seg_info, const int* tiles, int n_tiles, const int* block_table,
+                                 int max_pages, int page_size, int q_heads, int kv_heads, int dk, int dv,
+                                 ScoreMod mod, const float* slopes, const void* gate, int gate_stride, void* out,
+                                 cudaStream_t stream) {
+    const size_t smem = (size_t)2 * kPfN * ((DKP + kPfPad) + (DVP + kPfPad)) * 2;
+    static OncePerDevice configured;
+    if (configured.first()) {
+        cudaError_t e = cudaFuncSetAttribute(attention_biased_prefill_kernel<DKP, DVP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_error("attention_biased_prefill: %s", cudaGetErrorString(e)); return (int)e; }
+        configured.done();
+    }
+    launch_pdl(kPdlAttention, attention_biased_prefill_kernel<DKP, DVP>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32),
+               smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, seg_info, tiles,
+               block_table, max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
+               gate_stride, (bf16*)out);
+    return finish_launch("attention_biased_prefill");
+}
+
+// ---------------------------------------------------------------- one-token rows, bfloat16
+// One block per (row, key/value head).  A key is read once for all GS query heads of the group, by
+// LPK lanes with 16 bytes each; a warp therefore walks 32 / LPK keys at a time, four warps a block.
+// Every such stream of keys keeps its own running maximum, sum and value sums; they meet in shared
+// memory at the end, in the order of the streams.
+constexpr int kDecWarps = 4;
+
+template <int GS, int LPK>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
+                               const int* __restrict__ positions, const int* __restrict__ token_slot,
+                               const int* __restrict__ rows, const int* __restrict__ block_table, int max_pages,
+                               int page_size, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
+                               const float* __restrict__ slopes, const bf16* gate, int gate_stride,
+                               bf16* __restrict__ out) {
+    extern __shared__ float dec_smem[];
+    TLLM_PDL_ENTER();
+    constexpr int kStreams = kDecWarps * (32 / LPK);
+    const int t = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+    const int g = blockIdx.y;
+    const int group = q_heads / kv_heads;
+    const int head0 = g * group;
+    const int slot = token_slot[t];
+    if (slot < 0) {
+        for (int i = threadIdx.x; i < group * dv; i += blockDim.x)
+            out[((size_t)t * q_heads + head0) * dv + i] = __float2bfloat16_rn(0.0f);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / LPK, li = lane % LPK;
+    const int stream = warp * (32 / LPK) + sub;
+    const int pos = positions[t];
+    const int lo = first_key(pos, mod);
+    const int* table = block_table + (size_t)slot * max_pages;
+    const bool has_k = li * 8 < dk, has_v = li * 8 < dv;
+
+    float qf[GS][8], slope[GS];
+#pragma unroll
+    for (int h = 0; h < GS; ++h) {
+        slope[h] = (slopes != nullptr && h < group) ? slopes[head0 + h] : 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qf[h][e] = 0.0f;
+        if (h < group && has_k) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(q + ((size_t)t * q_heads + head0 + h) * dk + li * 8);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(p2[e]);
+                qf[h][2 * e] = f.x;
+                qf[h][2 * e + 1] = f.y;
+            }
+        }
+    }
+    float m[GS], l[GS], acc[GS][8];
+#pragma unroll
+    for (int h = 0; h < GS; ++h) {
+        const bool first = mod.sink && stream == 0;
+        m[h] = first ? 0.0f : -INFINITY;
+        l[h] = first ? 1.0f : 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
+    }
+    // the warp's lanes walk the loop together (the shuffles below take all of them); a stream whose key
+    // lies past the row's own position idles in the last round
+    for (int j0 = lo + warp * (32 / LPK); j0 <= pos; j0 += kStreams) {
+        const int j = j0 + sub;
+        const int page = j <= pos ? table[j / page_size] : -1;
+        const bool ok = page >= 0;
+        const long long base = (long long)(ok ? page : 0) * page_stride;
+        const size_t in_page = (size_t)g * page_size + (j % page_size);
+        uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
+        if (ok && has_k) kraw = *reinterpret_cast<const uint4*>(k_plane + base + in_page * dk + li * 8);
+        if (ok && has_v) vraw = *reinterpret_cast<const uint4*>(v_plane + base + in_page * dv + li * 8);
+        float kf[8], vf[8];
+        {
+            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw);
+            const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(k2[e]), b = __bfloat1622float2(v2[e]);
+                kf[2 * e] = a.x; kf[2 * e + 1] = a.y;
+                vf[2 * e] = b.x; vf[2 * e + 1] = b.y;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < GS; ++h) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dot += qf[h][e] * kf[e];
+#pragma unroll
+            for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
+            if (!ok) continue;             // uniform within the key's lanes
+            const float sc = mod_score(dot, slope[h], pos - j, mod);
+            const float m_new = fmaxf(m[h], sc);
+            const float corr = expf(m[h] - m_new), p = expf(sc - m_new);
+            l[h] = l[h] * corr + p;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] = acc[h][e] * corr + p * vf[e];
+            m[h] = m_new;
+        }
+    }
+    // streams meet: [stream][head][dv + 2]
+    const int rec = dv + 2;
+#pragma unroll
+    for (int h = 0; h < GS; ++h) {
+        if (h >= group) continue;
+        float* dst = dec_smem + ((size_t)stream * group + h) * rec;
+        if (has_v) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[li * 8 + e] = acc[h][e];
+        }
+        if (li == 0) { dst[dv] = m[h]; dst[dv + 1] = l[h]; }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * dv; i += blockDim.x) {
+        const int h = i / dv, e = i % dv;
+        float mm = -INFINITY;
+        for (int s2 = 0; s2 < kStreams; ++s2) mm = fmaxf(mm, dec_smem[((size_t)s2 * group + h) * rec + dv]);
+        float total = 0.0f, v = 0.0f;
+        for (int s2 = 0; s2 < kStreams; ++s2) {
+            const float* src = dec_smem + ((size_t)s2 * group + h) * rec;
+            const float w = src[dv] == -INFINITY ? 0.0f : expf(src[dv] - mm);
+            total += src[dv + 1] * w;
+            v += src[e] * w;
+        }
+        v = total > 0.0f ? v / total : 0.0f;
+        if (gate != nullptr)
+            v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)(head0 + h) * dv + e])));
+        out[((size_t)t * q_heads + head0 + h) * dv + e] = __float2bfloat16_rn(v);
+    }
+}
+
+template <int GS, int LPK>
+static int launch_biased_decode(const void* q, const void* kp, const void* vp, long long page_stride,
+                                const int* positions, const int* token_slot, const int* rows, int n_rows,
+                                const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads,
+                                int dk, int dv, ScoreMod mod, const float* slopes, const void* gate,
+                                int gate_stride, void* out, cudaStream_t stream) {
+    const int streams = kDecWarps * (32 / LPK);
+    const size_t smem = (size_t)streams * (q_heads / kv_heads) * (dv + 2) * sizeof(float);
+    static OncePerDevice configured;
+    if (configured.first()) {
+        cudaError_t e = cudaFuncSetAttribute(attention_biased_decode_kernel<GS, LPK>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) { set_error("attention_biased_decode: %s", cudaGetErrorString(e)); return (int)e; }
+        configured.done();
+    }
+    launch_pdl(kPdlAttention, attention_biased_decode_kernel<GS, LPK>, dim3(n_rows, kv_heads), dim3(kDecWarps * 32),
+               smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, positions, token_slot,
+               rows, block_table, max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
+               gate_stride, (bf16*)out);
+    return finish_launch("attention_biased_decode");
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -266,6 +645,55 @@ int tllm_attention_biased_general(
         return launch_general<float>(q, k_plane, v_plane, page_stride, positions, token_slot, block_table, max_pages,
                                      page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream);
     TLLM_REQUIRE(false, "attention_biased: unknown dtype %d", dtype);
+}
+
+// Whether the two bfloat16 kernels below take these sizes (else the general kernel serves).
+int tllm_attention_biased_fast_ok(int q_heads, int kv_heads, int dk, int dv) {
+    return q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 8 &&
+           dk % 8 == 0 && dv % 8 == 0 && dk > 0 && dv > 0 && dk <= 128 && dv <= 128;
+}
+
+// seg_info: int[segments][4] = slot, first row, length, position of the first row.
+// tiles: int[n_tiles][2] = segment, offset of the block's first query row in the segment.
+int tllm_attention_biased_prefill(
+    const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* seg_info,
+    const int* tiles, int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
+    int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
+    const float* slopes, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_prefill: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
+    TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_tiles >= 0 && q_heads <= 65535, "attention_biased_prefill: bad geometry");
+    TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_prefill: negative constant");
+    TLLM_REQUIRE(gate == nullptr || gate_stride % 2 == 0, "attention_biased_prefill: odd gate stride");
+    if (n_tiles == 0) return 0;
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
+#define PF(A, B) launch_biased_prefill<A, B>(q, k_plane, v_plane, page_stride, seg_info, tiles, n_tiles, block_table, max_pages, \
+                                             page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream)
+    if (dk <= 64) return dv <= 64 ? PF(64, 64) : PF(64, 128);
+    return dv <= 64 ? PF(128, 64) : PF(128, 128);
+#undef PF
+}
+
+// rows: indices of the one-token rows (null: rows 0 .. n_rows - 1).
+int tllm_attention_biased_decode(
+    const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
+    const int* token_slot, const int* rows, int n_rows, const int* block_table, int max_pages, int page_size,
+    int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
+    const float* slopes, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_decode: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
+    TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_rows >= 0 && kv_heads <= 65535, "attention_biased_decode: bad geometry");
+    TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_decode: negative constant");
+    if (n_rows == 0) return 0;
+    const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
+    const int group = q_heads / kv_heads;
+    const int wide = dk > dv ? dk : dv;
+#define DEC(G, L) launch_biased_decode<G, L>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
+                                             max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream)
+#define DEC_G(L) (group <= 1 ? DEC(1, L) : group <= 2 ? DEC(2, L) : group <= 4 ? DEC(4, L) : DEC(8, L))
+    if (wide <= 32) return DEC_G(4);
+    if (wide <= 64) return DEC_G(8);
+    return DEC_G(16);
+#undef DEC_G
+#undef DEC
 }
 
 }  // extern "C"

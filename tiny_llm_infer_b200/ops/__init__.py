@@ -67,6 +67,10 @@ def _declare(h) -> None:
                                 i32, i32, i32, i32, i32, vp],
         "tllm_attention_biased_general": [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32,
                                           f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+        "tllm_attention_biased_prefill": [vp, vp, vp, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
+                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+        "tllm_attention_biased_decode": [vp, vp, vp, i64, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
+                                         f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
         "tllm_moe_route": [vp, i32, i32, i32, i32, vp, vp, vp],
         "tllm_moe_plan": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
         "tllm_moe_grouped": [vp, i32, vp, vp, i32, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
@@ -97,6 +101,8 @@ def _declare(h) -> None:
         fn = getattr(h, name)
         fn.argtypes = args
         fn.restype = i32
+    h.tllm_attention_biased_fast_ok.argtypes = [i32, i32, i32, i32]
+    h.tllm_attention_biased_fast_ok.restype = i32
     h.tllm_moe_tile_rows.argtypes = []
     h.tllm_moe_tile_rows.restype = i32
     h.tllm_paged_attention_prefill_tc_rows.argtypes = [i32, i32]
@@ -588,6 +594,9 @@ def _plane(plane: torch.Tensor):
     return plane.data_ptr(), plane.stride(0)
 
 
+BIASED_FAST = True       # False: every row takes the general kernel (for comparisons)
+
+
 def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slot, block_table,
                    k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], page_size: int,
                    q_heads: int, kv_heads: int, dk: int, dv: int, eps: Optional[float],
@@ -634,6 +643,22 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         gate_stride = gate.stride(0)
     if slopes is not None:
         assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
+    gate_ptr = None if gate is None else gate.data_ptr()
+    consts = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
+              gate_ptr, gate_stride, _p(out), _stream())
+    if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
+            and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 \
+            and lib().tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv):
+        # one-token rows: keys read once per group of query heads; longer portions: tensor-core tiles
+        if ctx.n_dec:
+            _check(lib().tllm_attention_biased_decode(
+                _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(ctx.dec_rows), ctx.n_dec, _p(block_table),
+                block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *consts), "attention_biased_decode")
+        if ctx.n_tiles:
+            _check(lib().tllm_attention_biased_prefill(
+                _p(q), kp, vp, stride, _p(ctx.seg_info), _p(ctx.pf_tiles), ctx.n_tiles, _p(block_table),
+                block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *consts), "attention_biased_prefill")
+        return out
     _check(lib().tllm_attention_biased_general(
         _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(block_table), block_table.shape[1], page_size,
         _dt(q), tokens, q_heads, kv_heads, dk, dv, float(scale), float(softcap or 0.0), int(chunk or 0),
