@@ -397,6 +397,258 @@ def precheck(model, cfg, sizes, device) -> dict:
     return out
 
 
+
+# ---------------------------------------------------------------------- a design beside its closest relative
+DESIGN_SIZES = {
+    # width, heads, kv heads, head width, dense ff; experts, top, expert ff, shared ff (top * expert + shared = dense ff,
+    # so that a token costs the same in a mixture layer as in a dense one); chunk of the attention mask
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=6144, experts=32, top=4, expert_ff=1024, shared_ff=2048,
+               chunk=2048, layers=8, vocab=32768),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, experts=64, top=4, expert_ff=2048, shared_ff=4096,
+               chunk=4096, layers=4, vocab=32768),
+}
+
+
+def design_bench(args) -> int:
+    """``--design panolorn``: prefill and decode throughput of the Panolorn design at sizes that resemble a
+    real model's layers (random weights, bfloat16; layers alternate dense and mixture feed-forwards), beside
+    Qwen3 dense, the closest model the engine has, at equal sizes (same width, heads, head width, layers,
+    vocabulary, and a feed-forward as wide as a token's share of the mixture), through the same step
+    function; and the new kernels one by one beside their relatives, with their share of the measured
+    peaks.  One JSON line."""
+    import math
+    import torch
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.config.panolorn import (AttentionMixerConfig, FeedForwardConfig, PanolornConfig,
+                                                      PanolornLayerConfig)
+    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, random_model
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    device = "cuda:0"
+    pk = peaks()
+    ops.lib()
+    gen = torch.Generator().manual_seed(0)
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+    tokens_pf, batch, context = 2048, args.batch, 2048
+    steps, warmup = max(4, min(args.steps, 32)), max(args.warmup, 3)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)      # larger than L2
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return statistics.median(out)
+
+    def run_model(cfg, name, params, kv_bytes_per_token):
+        model = random_model(cfg, seed=0, dtype=torch.bfloat16, device=device, std=0.02)
+        page = 16
+        pages = (batch + 1) * (context // page) + 2 * (tokens_pf // page) + 64
+        cache = CacheManager(model.cache_needs(), page, pages, max_slots=batch + 1, max_seq_len=context + 64,
+                             dtype=torch.bfloat16, device=device)
+        runner = ModelRunner(model, cache, max_batch_tokens=tokens_pf)
+        vocab = cfg.vocab_size
+
+        def toks(n):
+            return torch.randint(0, vocab, (n,), generator=gen).tolist()
+
+        def prefill_once():
+            runner.step([StepEntry("pf", toks(tokens_pf), [tokens_pf - 1])])
+            torch.cuda.synchronize()
+            runner.release("pf")
+
+        w0 = time.perf_counter()
+        pf_ms = timed(prefill_once)
+        windows.append((w0, time.perf_counter(), f"{name} prefill"))
+        start_len = context - steps - warmup
+        names = [f"d{i}" for i in range(batch)]
+        for n in names:
+            runner.step([StepEntry(n, toks(start_len), [])])
+        w0 = time.perf_counter()
+        times = []
+        before = ops.launches
+        for it in range(warmup + steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            nxt = toks(batch)
+            a.record()
+            logits = runner.step([StepEntry(n, [t], [0]) for n, t in zip(names, nxt)])
+            b.record()
+            torch.cuda.synchronize()
+            if it == warmup - 1:
+                before = ops.launches
+            if it >= warmup:
+                times.append(a.elapsed_time(b))
+        launches = ops.launches - before
+        windows.append((w0, time.perf_counter(), f"{name} decode"))
+        assert bool(torch.isfinite(logits).all())
+        dec_ms = statistics.median(times)
+        for n in names:
+            runner.release(n)
+        runner.check_kernels()
+        out = {"prefill_tokens_per_s": round(tokens_pf / pf_ms * 1e3, 1), "prefill_ms": round(pf_ms, 3),
+               "prefill_tflops": round(2.0 * tokens_pf * params["active"] / pf_ms / 1e9, 1),
+               "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1), "decode_ms": round(dec_ms, 4),
+               "decode_gbs": round((2.0 * params["read"] + batch * context * kv_bytes_per_token) / dec_ms / 1e6, 1),
+               "launches_per_decode_step": launches // max(steps, 1)}
+        del runner, cache, model
+        torch.cuda.empty_cache()
+        return out
+
+    record = {"sizes": {}}
+    for size_name in ([args.model] if args.model in DESIGN_SIZES else sorted(DESIGN_SIZES)):
+        z = DESIGN_SIZES[size_name]
+        L, W, H, G, D = z["layers"], z["width"], z["heads"], z["kv_heads"], z["dim"]
+        mixer = AttentionMixerConfig(H, G, D, D, 1.0 / math.sqrt(D), 50.0, z["chunk"])
+        dense = FeedForwardConfig("dense", z["ff"])
+        moe = FeedForwardConfig("moe", z["expert_ff"], experts=z["experts"], top=z["top"], shared_ff=z["shared_ff"])
+        pcfg = PanolornConfig(vocab=z["vocab"], width=W, embedding_scale=math.sqrt(W), norm_eps=1e-5, layers=tuple(
+            PanolornLayerConfig("attention", mixer, dense if i % 2 == 0 else moe) for i in range(L)))
+        qcfg = Qwen3Config(hidden_size=W, intermediate_size=z["ff"], num_hidden_layers=L, num_attention_heads=H,
+                           num_key_value_heads=G, head_dim=D, vocab_size=z["vocab"], max_position_embeddings=8192,
+                           tie_word_embeddings=True, layer_types=("full_attention",) * L)
+        attn = W * (H + 2 * G) * D + H * D * W
+        gate = W * H * D
+        p_active = L * (attn + gate + 3 * W * z["ff"]) + (L // 2) * W * z["experts"] + z["vocab"] * W
+        # weights a decode step of `batch` rows reads: at most batch * top experts of a mixture layer
+        hit = min(z["experts"], batch * z["top"])
+        p_read = L * (attn + gate) + (L - L // 2) * 3 * W * z["ff"] \
+            + (L // 2) * (3 * W * (hit * z["expert_ff"] + z["shared_ff"]) + W * z["experts"]) + z["vocab"] * W
+        q_params = L * (attn + 3 * W * z["ff"]) + z["vocab"] * W
+        kv = 2 * G * D * 2 * L
+        print(f"[bench] design sizes {size_name}: Panolorn", file=sys.stderr, flush=True)
+        ours = run_model(pcfg, f"panolorn {size_name}", {"active": p_active, "read": p_read}, kv)
+        print(f"[bench] {ours}\n[bench] design sizes {size_name}: Qwen3 dense", file=sys.stderr, flush=True)
+        theirs = run_model(qcfg, f"qwen3 {size_name}", {"active": q_params, "read": q_params}, kv)
+        print(f"[bench] {theirs}", file=sys.stderr, flush=True)
+        for r in (ours, theirs):
+            r["prefill_frac_of_measured"] = round(r["prefill_tflops"] / pk["bf16_tflops"], 4)
+            r["decode_hbm_frac_of_measured"] = round(r["decode_gbs"] / pk["hbm_gbs"], 4)
+        record["sizes"][size_name] = {"panolorn": ours, "qwen3_dense": theirs, "config": z}
+
+    # ---- kernels one by one at the larger sizes (inputs larger than L2 or L2 flushed between runs)
+    z = DESIGN_SIZES["8b"]
+    W, H, G, D = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    bf = torch.bfloat16
+    kern = {}
+    T = tokens_pf
+    # norm of the sub-layer's output + sum + next norm, beside the sum + norm of the other block
+    h = torch.randn(T * 4, W, device=device)
+    delta = torch.randn(T * 4, W, device=device).to(bf)
+    gain = torch.ones(W, device=device, dtype=bf)
+    out = torch.empty_like(delta)
+    nbytes = h.numel() * 8 + delta.numel() * 4
+    for key, kw in (("add_rmsnorm", {}), ("postnorm_add_rmsnorm", dict(post_gain=gain, post_eps=1e-5))):
+        ms = timed(lambda: ops.add_rmsnorm(h, delta, gain, 1e-5, out, **kw))
+        kern[key] = {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+    del h, delta, out
+    # attention over a paged cache: prompt of 2048 tokens, and 64 one-token rows at context 2048
+    page, ctx_len, rows = 16, 2048, 64
+    n_pages = rows * ctx_len // page
+    flat = (torch.randn(n_pages, page * 2 * G * D, device=device) * 0.5).to(bf)
+    kv_u = flat.view(n_pages, 2, G, page, D)
+    k_plane = flat[:, :G * page * D].unflatten(1, (G, page, D))
+    v_plane = flat[:, G * page * D:].unflatten(1, (G, page, D))
+    table = torch.arange(n_pages, dtype=torch.int32, device=device).view(rows, ctx_len // page).contiguous()
+    slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / H) for i in range(H)], dtype=torch.float32, device=device)
+    from tiny_llm_infer_b200.engine.batch import StepContext
+
+    def context_for(segs):
+        seg, tiles, dec, row = [], [], [], 0
+        for s, (slot, p0, n) in enumerate(segs):
+            seg.append([slot, row, n, p0])
+            if n == 1:
+                dec.append(row)
+            else:
+                tiles += [(s, off) for off in range(0, n, 64)]
+            row += n
+        tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0))
+        pos = torch.tensor([p0 + i for _, p0, n in segs for i in range(n)], dtype=torch.int32, device=device)
+        slot = torch.tensor([sl for sl, _, n in segs for _ in range(n)], dtype=torch.int32, device=device)
+        return StepContext(tokens=row, token_ids=None, positions=pos, token_slot=slot, want_rows=None, segments=[],
+                           seg_info=torch.tensor(seg, dtype=torch.int32, device=device),
+                           dec_rows=None if len(dec) == row else torch.tensor(dec, dtype=torch.int32, device=device),
+                           n_dec=len(dec), pf_tiles=torch.tensor(tiles, dtype=torch.int32, device=device).view(-1, 2),
+                           n_tiles=len(tiles), n_tiles128=sum(1 for t in tiles if t[1] % 128 == 0),
+                           n_tiles256=sum(1 for t in tiles if t[1] % 256 == 0), max_context=ctx_len, max_segment=max(n for _, _, n in segs))
+
+    for what, segs in (("prefill_2048", [(0, 0, T)]), ("decode_64_rows_ctx_2048", [(i, ctx_len - 1, 1) for i in range(rows)])):
+        ctx = context_for(segs)
+        n = ctx.tokens
+        q = (torch.randn(n, H * D, device=device)).to(bf)
+        gate_t = torch.randn(n, H * D, device=device).to(bf)
+        o = torch.empty_like(q)
+        if n > 1 and what.startswith("prefill"):
+            flops = 4.0 * H * D * T * (T + 1) / 2
+            unit = lambda ms: {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1), "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+        else:
+            nbytes = rows * ctx_len * 2 * G * D * 2
+            unit = lambda ms: {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+        ms = timed(lambda: ops.attention_biased(q, k_plane, v_plane, ctx.positions, ctx.token_slot, table, page, H, G, D, D,
+                                                1.0 / math.sqrt(D), o, softcap=50.0, chunk=z["chunk"], sink=True, slopes=slopes,
+                                                gate=gate_t, ctx=ctx))
+        kern[f"attention_biased_{what}"] = unit(ms)
+        ms = timed(lambda: ops.paged_attention(q, kv_u, ctx.positions, ctx.token_slot, table, page, H, G, D, None,
+                                               1.0 / math.sqrt(D), o, ctx=ctx))
+        kern[f"paged_attention_{what}"] = unit(ms)
+    ops.check_error_word(device)
+    del flat, kv_u, k_plane, v_plane
+    # the experts' products beside the dense products of the same work
+    E, top, I = z["experts"], z["top"], z["expert_ff"]
+    x = torch.randn(T, W, device=device).to(bf)
+    w_gu = (torch.randn(E, 2 * I, W, device=device) * 0.02).to(bf)
+    w_d = (torch.randn(E, W, I, device=device) * 0.02).to(bf)
+    zr = torch.randn(T, E, device=device)
+    ids, wts = ops.moe_route(zr, top)
+    plan = ops.MoePlan(ids, E)
+    flops = 2.0 * T * top * 3 * W * I
+
+    def experts():
+        a = ops.moe_grouped(x, w_gu, plan, top, gated=True, gather=True, weights=wts)
+        return ops.moe_grouped(a, w_d, plan, top, gated=False, gather=False)
+    ms = timed(experts)
+    kern["moe_grouped_products_2048_tokens"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                                "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+    wd_gu = ops.interleave_gate_up(*(torch.randn(2, top * I, W, device=device) * 0.02).to(bf)).contiguous()
+    wd_d = (torch.randn(W, top * I, device=device) * 0.02).to(bf)
+    ms = timed(lambda: ops.linear(ops.linear_swiglu(x, wd_gu, bf, interleaved=True), wd_d, out_dtype=bf))
+    kern["dense_products_same_work_2048_tokens"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                                    "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+    x8 = x[:8].contiguous()
+    ids8, wts8 = ops.moe_route(zr[:8].contiguous(), top)
+    plan8 = ops.MoePlan(ids8, E)
+    nbytes = 8 * top * 3 * W * I * 2           # 32 different experts at most
+
+    def experts8():
+        a = ops.moe_grouped(x8, w_gu, plan8, top, gated=True, gather=True, weights=wts8)
+        return ops.moe_grouped(a, w_d, plan8, top, gated=False, gather=False)
+    ms = timed(experts8)
+    kern["moe_grouped_products_8_rows"] = {"us": round(ms * 1e3, 1), "gbs_at_most": round(nbytes / ms / 1e6, 1)}
+    ms = timed(lambda: ops.linear(ops.linear_swiglu(x8, wd_gu, bf, interleaved=True), wd_d, out_dtype=bf))
+    kern["dense_products_8_rows_of_one_expert_set"] = {"us": round(ms * 1e3, 1), "gbs": round(top * 3 * W * I * 2 / ms / 1e6, 1)}
+    ops.check_error_word(device)
+    record["kernels"] = kern
+    clock_record = clocks.stop(windows)
+    first = record["sizes"][sorted(record["sizes"])[0]]["panolorn"]
+    print(json.dumps({"metric": f"decode tok/s @ batch {batch} (Panolorn design sizes, context {context}, 1 B200)",
+                      "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": first["decode_ms"], "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "design": "panolorn", "clocks": clock_record, "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                      **record}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,7 +656,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--model", default="8b", choices=sorted(MODELS),
+    ap.add_argument("--model", default="8b", choices=sorted(set(MODELS) | set(DESIGN_SIZES)),
                     help="the sizes: 8b is the benchmark configuration, 0.6b and 32b the other two the reference is quoted on")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record) if memory or time needs it")
@@ -417,9 +669,19 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the logits check before the timed phases")
     ap.add_argument("--ref-all", action="store_true",
                     help="reference arm: its model_main --bench at batch 1, 8 and 64 instead of --batch alone")
+    ap.add_argument("--design", default=None, choices=["panolorn"],
+                    help="instead of the default workload: this design's prefill and decode throughput at sizes that "
+                         "resemble a real model's layers beside Qwen3 dense at equal sizes, and its kernels one by one")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed", "p128"],
                     help="run one phase only (for profiling a small case); the record then lacks the others")
     args = ap.parse_args()
+    if args.design is not None:
+        if args.gpus != 1 or args.impl != "ours":
+            print("bench.py: --design runs this engine on one GPU")
+            return 2
+        return design_bench(args)
+    if args.model not in MODELS:
+        ap.error(f"--model {args.model} goes with --design")
     model_name, model_sizes = MODELS[args.model]
     if args.layers is None:
         args.layers = model_sizes["num_hidden_layers"]

@@ -121,8 +121,20 @@ def router(u, w_router, top):
     return idx, weights
 
 
-def moe(u, w, prefix, mlp):
+def router_gaps(u, w_router, top):
+    """Per token, how far the last chosen expert's logit lies above the best one left out, in units of
+    the logits' spread (infinite when every expert is chosen)."""
+    z = u @ w_router.t()
+    if top >= z.shape[-1]:
+        return torch.full((u.shape[0],), float("inf"), dtype=F)
+    ordered = torch.sort(z, dim=-1, descending=True).values
+    return (ordered[:, top - 1] - ordered[:, top]) / z.std()
+
+
+def moe(u, w, prefix, mlp, gaps_out=None):
     idx, weights = router(u, w[prefix + "router"], mlp["router"]["top"])
+    if gaps_out is not None:
+        gaps_out.append(router_gaps(u, w[prefix + "router"], mlp["router"]["top"]))
     out = torch.zeros_like(u)
     for t in range(u.shape[0]):
         for e, s in zip(idx[t].tolist(), weights[t]):
@@ -132,17 +144,17 @@ def moe(u, w, prefix, mlp):
     return out
 
 
-def feed_forward(u, w, prefix, mlp):
+def feed_forward(u, w, prefix, mlp, gaps_out=None):
     if mlp["kind"] == "dense":
         return gated_mlp(u, w, prefix, gelu_tanh)
     if mlp["kind"] == "moe":
-        return moe(u, w, prefix, mlp)
+        return moe(u, w, prefix, mlp, gaps_out)
     raise ValueError(mlp["kind"])
 
 
-def forward(cfg, w, tokens, layers_out=None):
+def forward(cfg, w, tokens, layers_out=None, gaps_out=None):
     """Logits [T, vocab] float64 of one whole sequence; ``layers_out`` (a list) receives the
-    residual stream after every layer."""
+    residual stream after every layer, ``gaps_out`` (a list) every router's ``router_gaps``."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(list(tokens))] * cfg["embedding"]["scale"]
     for i, layer in enumerate(cfg["layers"]):
@@ -152,8 +164,28 @@ def forward(cfg, w, tokens, layers_out=None):
         a = attention_mixer(rms_norm(x, w[p + "norm1"], eps), w, p + "mix.", layer["mixer"], eps)
         x = x + rms_norm(a, w[p + "norm1b"], eps)
         if layer.get("mlp"):
-            m = feed_forward(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            m = feed_forward(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], gaps_out)
             x = x + rms_norm(m, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["embed"].t()
+
+
+def decisive_tokens(cfg, w, tokens, seed, threshold=0.08, tries=400):
+    """``tokens`` with some of them drawn again until no router of the model meets a near-tie anywhere
+    in the sequence (every gap of ``router_gaps`` above ``threshold``).  In 16-bit arithmetic a near-tie
+    falls either way, and the row then differs by a whole expert; a comparison of logits wants prompts
+    on which the design's answer does not hang on the last bit.  Tokens before the first near-tie stay
+    as they are (the model is causal), so the search moves from left to right."""
+    g = torch.Generator().manual_seed(seed)
+    tokens = list(tokens)
+    for _ in range(tries):
+        gaps = []
+        forward(cfg, w, tokens, gaps_out=gaps)
+        if not gaps:
+            return tokens
+        close = (torch.stack(gaps).min(0).values < threshold).nonzero().flatten()
+        if close.numel() == 0:
+            return tokens
+        tokens[int(close[0])] = int(torch.randint(0, cfg["vocab"], (1,), generator=g))
+    raise RuntimeError("no sequence without near-ties found")

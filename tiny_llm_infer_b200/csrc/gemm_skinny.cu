@@ -56,7 +56,7 @@ struct SkinnyStage {
 // inlined, the SwiGLU form costs the kernel ten registers more than the plain one (88 instead of
 // 78) and with them the third block per SM (the gate/up product of Qwen3-8B sizes: 42.5 us at two
 // blocks per SM, 35.1 at three, as the plain product of the same rows).
-template <int NT, typename TOut, bool SWIGLU>
+template <int NT, typename TOut, bool SWIGLU, int ACT>
 __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut* y, int M, int N, int r0) {
     constexpr int kRows = SWIGLU ? 8 : 16;                   // output columns of the block
     for (int idx = threadIdx.x; idx < kRows * NT * 8; idx += blockDim.x) {
@@ -69,7 +69,7 @@ __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut*
                 float up = 0.0f;
 #pragma unroll
                 for (int ww = 0; ww < kSkinnyWarps; ++ww) up += red[ww][row + 8][tok];
-                s = s / (1.0f + expf(-s)) * up;
+                s = gate_act(s, ACT) * up;
             }
             y[(size_t)tok * N + r0 + row] = from_f32<TOut>(s);
         }
@@ -81,7 +81,7 @@ __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut*
 // that belong to them as its lower half, so that a gate sum and its up sum meet in one thread's
 // accumulator; it writes silu(gate) * up: y is [M, N].  The grid, the bytes per block, the memory
 // pattern and the registers are those of the plain product of the 2 N rows.
-template <int NT, typename TOut, bool SWIGLU, int STAGES>
+template <int NT, typename TOut, bool SWIGLU, int STAGES, int ACT>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
@@ -167,10 +167,10 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
         red[warp][rq + 8][nt * 8 + c * 2 + 1] = acc[nt][3];
     }
     __syncthreads();
-    skinny_epilogue<NT, TOut, SWIGLU>(red, y, M, N, r0);
+    skinny_epilogue<NT, TOut, SWIGLU, ACT>(red, y, M, N, r0);
 }
 
-template <int NT, typename TOut, bool SWIGLU, int STAGES = 3>
+template <int NT, typename TOut, bool SWIGLU, int STAGES = 3, int ACT = kActSilu>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(SWIGLU ? (N + 7) / 8 : (N + 15) / 16);
@@ -182,7 +182,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU, STAGES>, (const bf16*)x, (const bf16*)w,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU, STAGES, ACT>, (const bf16*)x, (const bf16*)w,
                                        (TOut*)y, M, N, K);
     if (e != cudaSuccess) {
         set_error("gemm_skinny: %s", cudaGetErrorString(e));
@@ -228,10 +228,11 @@ extern "C" int tllm_gemm_skinny(const void* x, const void* w, void* y, int out_d
     return launch_skinny<4, float, false>(x, w, y, M, N, K, stream);
 }
 
-// y[M, N] = silu(x . gate^T) * (x . up^T) for w of 2 N rows, gate and up interleaved by eight
+// y[M, N] = act(x . gate^T) * (x . up^T), act silu or the tanh form of GELU, for w of 2 N rows, gate and up interleaved by eight
 // (eight gate rows, their eight up rows, ...), bfloat16 out, M <= 16.
-extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K,
+extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, int M, int N, int K, int act,
                                        cudaStream_t stream) {
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_skinny_swiglu: unknown activation %d", act);
     TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_swiglu: bad sizes");
     TLLM_REQUIRE(M <= 16, "gemm_skinny_swiglu: %d rows exceed 16", M);
     TLLM_REQUIRE(N % 8 == 0, "gemm_skinny_swiglu: N = %d is no multiple of 8", N);
@@ -239,6 +240,10 @@ extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, in
     TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
                  "gemm_skinny_swiglu: operands must be 16-byte aligned");
     if (M == 0) return 0;
+    if (act == kActGeluTanh) {
+        if (M <= 8) return launch_skinny<1, bf16, true, 3, kActGeluTanh>(x, w, y, M, N, K, stream);
+        return launch_skinny<2, bf16, true, 3, kActGeluTanh>(x, w, y, M, N, K, stream);
+    }
     if (M <= 8) return launch_skinny<1, bf16, true>(x, w, y, M, N, K, stream);
     return launch_skinny<2, bf16, true>(x, w, y, M, N, K, stream);
 }

@@ -38,6 +38,17 @@ constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kSpinLimit = 1 << 20;
 
+// act(gate) of the gated epilogue with the fast intrinsics: silu g / (1 + e^-g), or the tanh form of GELU
+// written the same way, 0.5 g (1 + tanh(u)) = g / (1 + e^-2u) with u = sqrt(2/pi) (g + 0.044715 g^3).
+template <int ACT>
+__device__ __forceinline__ float fast_gate_act(float g) {
+    if (ACT == kActGeluTanh) {
+        const float u2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+        return __fdividef(g, 1.0f + __expf(-u2));
+    }
+    return __fdividef(g, 1.0f + __expf(-g));
+}
+
 __device__ __forceinline__ uint32_t cvta_shared(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -152,7 +163,7 @@ __device__ __forceinline__ void store_row32(bf16* row_ptr, int col0, int cols, c
 // owns 256 rows, both accumulators belong to one tile, every slab of W fetched from L2 feeds
 // twice as many MMAs (32 KB of shared-memory fill per 128 x 256 x 64 instead of 48 KB), three
 // stages of 64 KB; the epilogue is not overlapped.
-template <bool SWIGLU, int MT>
+template <bool SWIGLU, int MT, int ACT>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ y, int M, int N, int K, int half_n, int interleaved, int tiles_m,
@@ -302,8 +313,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                             for (int i = 0; i < 16; ++i) {
                                 const int gi = 16 * (i >> 3) + (i & 7);
                                 const float g0 = __uint_as_float(r0[gi]), g1 = __uint_as_float(r1[gi]);
-                                v[32 * h + i] = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(r0[gi + 8]);
-                                v[32 * h + 16 + i] = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(r1[gi + 8]);
+                                v[32 * h + i] = fast_gate_act<ACT>(g0) * __uint_as_float(r0[gi + 8]);
+                                v[32 * h + 16 + i] = fast_gate_act<ACT>(g1) * __uint_as_float(r1[gi + 8]);
                             }
                         }
                     } else if (SWIGLU) {
@@ -316,7 +327,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const float g = __uint_as_float(gr[i]);
-                                v[32 * h + i] = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(ur[i]);
+                                v[32 * h + i] = fast_gate_act<ACT>(g) * __uint_as_float(ur[i]);
                             }
                         }
                     } else {
@@ -410,13 +421,13 @@ static int sm_count() {
     return n;
 }
 
-template <bool SWIGLU, int MT>
+template <bool SWIGLU, int MT, int ACT = kActSilu>
 static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int M, int N, int K, int half_n,
                           int interleaved, int* error_word, cudaStream_t stream) {
     const size_t smem = (size_t)(MT == 1 ? 4 : 3) * (kBM * MT * kBK * 2 + kStageBBytes) + 1024 + 4 * 32 * (64 * 2 + 16);
     static OncePerDevice configured;
     if (configured.first()) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<SWIGLU, MT>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<SWIGLU, MT, ACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_error("gemm_tcgen05: %s", cudaGetErrorString(e)); return (int)e; }
         configured.done();
@@ -426,7 +437,7 @@ static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y,
     const int tiles_n = (out_cols + col_tile - 1) / col_tile, tiles_m = (M + kBM * MT - 1) / (kBM * MT);
     const int total = tiles_m * tiles_n;
     const int grid = total < sm_count() ? total : sm_count();
-    gemm_tcgen05_kernel<SWIGLU, MT><<<grid, kGemmThreads, smem, stream>>>(mx, mw, (bf16*)y, M, N, K, half_n, interleaved,
+    gemm_tcgen05_kernel<SWIGLU, MT, ACT><<<grid, kGemmThreads, smem, stream>>>(mx, mw, (bf16*)y, M, N, K, half_n, interleaved,
                                                                       tiles_m, tiles_n, error_word);
     return finish_launch("gemm_tcgen05");
 }
@@ -455,6 +466,11 @@ extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, i
     const bool tall = M > 128 && !(swiglu & 2) ;          // blocks of 256 rows once there are that many
     TLLM_REQUIRE(make_map(&mx, x, M, K, tall ? 2 * kBM : kBM) && make_map(&mw, w, N, K, 128),
                  "gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
+    const int act = swiglu >> 8;                            // bits 8 and up: the gate's activation (GateAct)
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tcgen05: unknown activation %d", act);
+    if ((swiglu & 1) && act == kActGeluTanh)
+        return tall ? launch_tcgen05<true, 2, kActGeluTanh>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream)
+                    : launch_tcgen05<true, 1, kActGeluTanh>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream);
     if (swiglu & 1)
         return tall ? launch_tcgen05<true, 2>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream)
                     : launch_tcgen05<true, 1>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream);

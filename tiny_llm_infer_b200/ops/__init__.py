@@ -90,7 +90,7 @@ def _declare(h) -> None:
         "tllm_gemm_skinny": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_plain": [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
-        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, vp],
+        "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -510,7 +510,7 @@ def tcgen05_pays(rows: int, out_cols: int, k: int, dtype, col_tile: int = 256) -
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, short_tiles: bool = False,
-                 interleaved: bool = False) -> torch.Tensor:
+                 interleaved: bool = False, act: str = "silu") -> torch.Tensor:
     """y = x . weight^T on tcgen05 tensor cores fed by TMA (csrc/gemm_tcgen05.cu), bfloat16 in
     and out, float32 accumulation in tensor memory.  With ``swiglu`` the weight is [gate; up]
     (or, ``interleaved``, gate and up rows interleaved by eight) and the result is
@@ -525,7 +525,7 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
         return y
     global tcgen05_calls
     tcgen05_calls += 1
-    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0) | (4 if interleaved else 0),
+    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0) | (4 if interleaved else 0) | (ACTIVATIONS[act] << 8 if swiglu else 0),
                                    _p(error_word(x.device)), _stream()), "gemm_tcgen05")
     return y
 
@@ -555,15 +555,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return torch.mm(x, weight.t(), out_dtype=want)
 
 
-def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) for at most 16 bfloat16 rows as one weight-streaming kernel;
     ``w_gate_up`` holds the rows of Wg and Wu interleaved by eight (``interleave_gate_up``)."""
     _cuda(x, w_gate_up)
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
-    act = torch.empty((rows, inter), dtype=torch.bfloat16, device=x.device)
-    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(act), rows, inter, k, _stream()), "gemm_skinny_swiglu")
-    return act
+    out = torch.empty((rows, inter), dtype=torch.bfloat16, device=x.device)
+    _check(lib().tllm_gemm_skinny_swiglu(_p(x), _p(w_gate_up), _p(out), rows, inter, k, ACTIVATIONS[act], _stream()),
+           "gemm_skinny_swiglu")
+    return out
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dtype,
@@ -575,11 +576,11 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out_dtype: torch.dty
     rows, k = x.shape
     inter = w_gate_up.shape[0] // 2
     plain = x.dtype == w_gate_up.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() \
-        and w_gate_up.is_contiguous() and act == "silu"
+        and w_gate_up.is_contiguous()
     if plain and tcgen05_pays(rows, inter, k, w_gate_up.dtype, col_tile=128):
-        return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved)
+        return gemm_tcgen05(x, w_gate_up, swiglu=True, interleaved=interleaved, act=act)
     if plain and interleaved and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0:
-        return gemm_skinny_swiglu(x, w_gate_up)
+        return gemm_skinny_swiglu(x, w_gate_up, act)
     gate_up = linear(x, w_gate_up, out_dtype=out_dtype)
     out = torch.empty((rows, inter), dtype=out_dtype, device=x.device)
     return swiglu(gate_up, out, interleaved, act)
