@@ -611,11 +611,12 @@ def design_bench(args) -> int:
     w_d = (torch.randn(E, W, I, device=device) * 0.02).to(bf)
     zr = torch.randn(T, E, device=device)
     ids, wts = ops.moe_route(zr, top)
-    plan = ops.MoePlan(ids, E)
+    on_tensor_memory = ops.moe_tcgen05_pays(T * top, E, I, W, bf)
+    plan = ops.MoePlan(ids, E, ops.MOE_TCGEN05_TILE if on_tensor_memory else None)
     flops = 2.0 * T * top * 3 * W * I
 
     def experts():
-        a = ops.moe_grouped(x, w_gu, plan, top, gated=True, gather=True, weights=wts)
+        a = ops.moe_grouped(x, w_gu, plan, top, gated=True, gather=True, weights=wts, interleaved=True)
         return ops.moe_grouped(a, w_d, plan, top, gated=False, gather=False)
     ms = timed(experts)
     kern["moe_grouped_products_2048_tokens"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
@@ -631,7 +632,7 @@ def design_bench(args) -> int:
     nbytes = 8 * top * 3 * W * I * 2           # 32 different experts at most
 
     def experts8():
-        a = ops.moe_grouped(x8, w_gu, plan8, top, gated=True, gather=True, weights=wts8)
+        a = ops.moe_grouped(x8, w_gu, plan8, top, gated=True, gather=True, weights=wts8, interleaved=True)
         return ops.moe_grouped(a, w_d, plan8, top, gated=False, gather=False)
     ms = timed(experts8)
     kern["moe_grouped_products_8_rows"] = {"us": round(ms * 1e3, 1), "gbs_at_most": round(nbytes / ms / 1e6, 1)}

@@ -221,7 +221,10 @@ def test_attention_kernels_over_scrambled_pages(case, dtype):
         before = ops.launches
         assert run(whole, fast=True) < tol
         fast_ok = bool(ops.lib().tllm_attention_biased_fast_ok(H, G, dk, dv))
-        assert ops.launches - before == (3 if fast_ok else 2)         # store + (decode and prefill | general)
+        reach = min(v for v in (case["chunk"], case["window"], 1 << 30) if v)
+        runs = ops.biased_decode_splits(1, G, reach)                  # the one-token request of the step
+        # store + (one-token kernel, the sum of its runs of keys if it has several, prompt kernel | general)
+        assert ops.launches - before == ((3 if runs == 1 else 4) if fast_ok else 2)
     # the cache is filled: portions that start anywhere, beside single rows at every kind of place
     edges = [p for p in (case["chunk"], case["window"], page) if p]
     singles = sorted({p for e in edges for p in (e - 1, e, e + 1, 2 * e - 1, 2 * e) if 0 < p < 150} | {149, 1})
@@ -301,14 +304,19 @@ def test_mixture_of_experts_alone(dtype, experts, top, shared, inter, hidden):
     part.load(dict(w))
     w64 = {"m." + k: v.double().cpu() for k, v in w.items()}
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "shared": {"ff": shared} if shared else None}
-    for rows in (1, 7, 150):
+    from tiny_llm_infer_b200 import ops
+    for rows in (1, 7, 150, 1100):                       # 1100: the grouped tcgen05 product where the sizes allow
         x = torch.randn(rows, hidden, generator=g).to(dtype).to(DEV)
+        before = ops.tcgen05_calls
         got = part.forward(x, None).double().cpu()
         want = plain.moe(x.double().cpu(), w64, "m.", mlp)
         tol = (1e-5 if dtype == torch.float32 else 0.03) * want.abs().max().item()
         bad = (got - want).abs().amax(1) > tol
         # bfloat16: the weight times the row is rounded before the product; a row may differ by that much, none by an expert
         assert not bad.any(), (rows, (got - want).abs().max().item(), tol)
+        on_tensor_memory = part.interleaved and ops.moe_tcgen05_pays(rows * top, experts, inter, hidden, dtype)
+        assert (ops.tcgen05_calls - before >= 2) == on_tensor_memory
+        ops.check_error_word(x.device)
 
 
 def test_router_takes_the_largest_and_the_lowest_index_on_ties():
@@ -420,6 +428,35 @@ def relative_rows_no_base(out, tb, want, vocab):
             if e > worst:
                 worst, where = e, (step, name, pos)
     return worst, where
+
+
+def test_experts_on_tcgen05_agree_with_the_mma_tiles_inside_a_model(tmp_path, monkeypatch):
+    """The same prompts through the model with the experts' products on the grouped tcgen05 kernel (its
+    threshold lowered for this) and on the mma.sync tiles: the logits agree as two bfloat16 paths do."""
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, load_model
+    tiny = PANOLORNS["P1"]
+    folder = make_folder(tiny, tmp_path)
+    cfg, w = plain.read_model(folder)
+    model, _ = load_model(folder, torch.bfloat16, DEV)
+    toks = plain.decisive_tokens(cfg, w, prompt(3, 200, cfg["vocab"]), seed=3)
+    want = plain.forward(cfg, w, toks).numpy()
+    got = {}
+    for rows in (64, 1 << 30):
+        monkeypatch.setattr(ops, "MOE_TCGEN05_ROWS", rows)
+        cache = CacheManager(model.cache_needs(), 16, 32, max_slots=2, max_seq_len=512, dtype=torch.bfloat16, device=DEV)
+        runner = ModelRunner(model, cache, max_batch_tokens=512)
+        before = ops.tcgen05_calls
+        got[rows] = runner.step([StepEntry("a", toks, list(range(len(toks))))]).double().cpu().numpy()
+        assert (ops.tcgen05_calls > before) == (rows == 64)
+        runner.check_kernels()
+    for a in got.values():
+        d = a - want
+        err = np.sqrt(((d - d.mean(1, keepdims=True)) ** 2).mean(1)) / want.std(1)
+        assert err.max() < BF16_RMS["P1"], err.max()
+    d = got[64] - got[1 << 30]
+    assert (np.sqrt((d ** 2).mean(1)) / want.std(1)).max() < BF16_RMS["P1"] / 2
 
 
 # ----------------------------------------------------------------------------- generation through the entry point

@@ -9,13 +9,13 @@
 // zero (or a null pointer) switches its step off, and with all of them off this is plain causal
 // attention.
 //
-// Three kernels.  `qkv_unit_store`: per-head RMS norm of queries and keys (with or without gains)
+// Four kernels.  `qkv_unit_store`: per-head RMS norm of queries and keys (with or without gains)
 // and the write of keys and values into their pages.  `attention_biased_general`: one block per
 // (token, query head), any widths up to 512, float32 or bfloat16; the float32 path and the fallback.
 // `attention_biased_prefill`: bfloat16 prompt portions on mma.sync tiles, 64 query rows of one head
 // per block, widths up to 128 (padded with zeros to 64 or 128 in shared memory).
-// `attention_biased_decode`: one-token rows, one block per (row, key/value head): the keys and values
-// are read once for all query heads of the group, 16 bytes per lane.
+// `attention_biased_decode`: one-token rows on the same tiles, one block per (row, key/value head, run of
+// keys): the query heads of the group are the rows of the tile, so keys and values are read once for all.
 //
 // Scores, the cap, the bias, the softmax and the gate are float32 in both storage types.  The order of
 // the additions for a (request, position, head) depends on the position and the constants only.
@@ -214,6 +214,22 @@ static int launch_general(const void* q, const void* kp, const void* vp, long lo
     return finish_launch("attention_biased_general");
 }
 
+constexpr float kLog2e = 1.4426950408889634f;
+
+// tanh(x) = 1 - 2 / (e^2x + 1): absolute error of a few 1e-7 with the fast exponential and division,
+// which the cap multiplies; |x| is clamped where tanh is 1 to the last bit anyway.
+__device__ __forceinline__ float fast_tanh(float x) {
+    x = fminf(fmaxf(x, -15.0f), 15.0f);
+    return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
+}
+
+// The modified score times log2(e), for exp2f.
+__device__ __forceinline__ float mod_score_fast(float dot, float slope, int dist, const ScoreMod& m) {
+    float s = dot * m.scale;
+    if (m.softcap > 0.0f) s = m.softcap * fast_tanh(__fdividef(s, m.softcap));
+    return (s - slope * (float)dist) * kLog2e;
+}
+
 // ---------------------------------------------------------------- prompt portions, bfloat16, mma.sync
 // A block owns 64 consecutive query rows of one portion and one query head and walks the keys its rows
 // can see in tiles of 64 (flash-attention style: S and the softmax in float32 registers, P V accumulated
@@ -222,7 +238,7 @@ static int launch_general(const void* q, const void* kp, const void* vp, long lo
 constexpr int kPfWarps = 4, kPfM = 64, kPfN = 64, kPfPad = 8;
 
 template <int DKP, int DVP>
-__global__ void __launch_bounds__(kPfWarps * 32)
+__global__ void __launch_bounds__(kPfWarps * 32, 2)
 attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
                                 const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                 const int* __restrict__ block_table, int max_pages, int page_size,
@@ -277,21 +293,27 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
         const uint32_t ks = smem_u32(pf_smem + (size_t)stage * (kKBytes + kVBytes));
         const uint32_t vs = ks + kKBytes;
         constexpr int kKC = DKP / 8, kVC = DVP / 8;
-        for (int c = threadIdx.x; c < kPfN * kKC; c += kPfWarps * 32) {
-            const int row = c / kKC, chunk = c % kKC;
+        // a thread keeps its 16-byte column and walks the rows: one look-up of the page per row
+        for (int row = threadIdx.x / kKC, chunk = threadIdx.x % kKC; row < kPfN; row += kPfWarps * 32 / kKC) {
             const int key = kt * kPfN + row;
             const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
-            const bool ok = page >= 0 && chunk * 8 < dk;
-            const bf16* src = k_plane + (ok ? (long long)page * page_stride + ((size_t)g * page_size + key % page_size) * dk + chunk * 8 : 0);
-            cp_async_16(ks + (row * kKRow + chunk * 8) * 2, src, ok);
+            const bool ok = page >= 0;
+            const long long page_at = ok ? (long long)page * page_stride : 0;
+            const long long in_page = (long long)g * page_size + key % page_size;
+            const bool k_ok = ok && chunk * 8 < dk;
+            cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
+            if (kKC == kVC) {
+                const bool v_ok = ok && chunk * 8 < dv;
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * dv + chunk * 8 : 0), v_ok);
+            }
         }
-        for (int c = threadIdx.x; c < kPfN * kVC; c += kPfWarps * 32) {
-            const int row = c / kVC, chunk = c % kVC;
-            const int key = kt * kPfN + row;
-            const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
-            const bool ok = page >= 0 && chunk * 8 < dv;
-            const bf16* src = v_plane + (ok ? (long long)page * page_stride + ((size_t)g * page_size + key % page_size) * dv + chunk * 8 : 0);
-            cp_async_16(vs + (row * kVRow + chunk * 8) * 2, src, ok);
+        if (kKC != kVC) {
+            for (int row = threadIdx.x / kVC, chunk = threadIdx.x % kVC; row < kPfN; row += kPfWarps * 32 / kVC) {
+                const int key = kt * kPfN + row;
+                const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
+                const bool v_ok = page >= 0 && chunk * 8 < dv;
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + key % page_size) * dv + chunk * 8 : 0), v_ok);
+            }
         }
         cp_async_commit();
     };
@@ -336,8 +358,8 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = key_base + nt * 8 + e;
-                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score(s[nt][e], slope, p_lo - j, mod) : -INFINITY;
-                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score(s[nt][2 + e], slope, p_hi - j, mod) : -INFINITY;
+                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score_fast(s[nt][e], slope, p_lo - j, mod) : -INFINITY;
+                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score_fast(s[nt][2 + e], slope, p_hi - j, mod) : -INFINITY;
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
                     tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
                 }
@@ -347,7 +369,7 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
             tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
             const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
             const float ms_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
-            const float c_lo = expf(m_lo - ms_lo), c_hi = expf(m_hi - ms_hi);
+            const float c_lo = exp2f(m_lo - ms_lo), c_hi = exp2f(m_hi - ms_hi);
             m_lo = mn_lo;
             m_hi = mn_hi;
             float sum_lo = 0.0f, sum_hi = 0.0f;
@@ -355,8 +377,8 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
             for (int nt = 0; nt < kPfN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    s[nt][e] = expf(s[nt][e] - ms_lo);
-                    s[nt][2 + e] = expf(s[nt][2 + e] - ms_hi);
+                    s[nt][e] = exp2f(s[nt][e] - ms_lo);
+                    s[nt][2 + e] = exp2f(s[nt][2 + e] - ms_hi);
                     sum_lo += s[nt][e];
                     sum_hi += s[nt][2 + e];
                 }
@@ -439,130 +461,217 @@ static int launch_biased_prefill(const void* q, const void* kp, const void* vp, 
     return finish_launch("attention_biased_prefill");
 }
 
-// ---------------------------------------------------------------- one-token rows, bfloat16
-// One block per (row, key/value head).  A key is read once for all GS query heads of the group, by
-// LPK lanes with 16 bytes each; a warp therefore walks 32 / LPK keys at a time, four warps a block.
-// Every such stream of keys keeps its own running maximum, sum and value sums; they meet in shared
-// memory at the end, in the order of the streams.
-constexpr int kDecWarps = 4;
-
-template <int GS, int LPK>
-__global__ void __launch_bounds__(kDecWarps * 32)
+// ---------------------------------------------------------------- one-token rows, bfloat16, mma.sync
+// One block per (row, key/value head, run of keys).  The query heads of the group are the 16 rows of the
+// tensor-core tile (the first `group` of them real), so keys and values are read once for all of them.
+// The block stages tiles of 64 keys like the prompt kernel; each of its four warps takes 16 keys of a
+// tile and keeps its own running maximum, sum and value sums (base 2), which meet in shared memory in
+// the order of the warps.  With one run per row the block writes the result; with more (a grid that
+// would not fill the GPU, long reaches) it leaves unnormalised sums, maximum and weight per run, and a
+// second kernel adds the runs in their order.  The sink belongs to the first warp of the first run.
+template <int DKP, int DVP>
+__global__ void __launch_bounds__(kPfWarps * 32, 2)
 attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
                                const int* __restrict__ positions, const int* __restrict__ token_slot,
                                const int* __restrict__ rows, const int* __restrict__ block_table, int max_pages,
                                int page_size, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
                                const float* __restrict__ slopes, const bf16* gate, int gate_stride,
-                               bf16* __restrict__ out) {
-    extern __shared__ float dec_smem[];
+                               int splits, float* part, bf16* __restrict__ out) {
+    extern __shared__ __align__(128) unsigned char pf_smem[];
     TLLM_PDL_ENTER();
-    constexpr int kStreams = kDecWarps * (32 / LPK);
+    constexpr int kKRow = DKP + kPfPad, kVRow = DVP + kPfPad;
+    constexpr int kKBytes = kPfN * kKRow * 2, kVBytes = kPfN * kVRow * 2;
     const int t = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
-    const int g = blockIdx.y;
+    const int g = blockIdx.y, split = blockIdx.z;
     const int group = q_heads / kv_heads;
     const int head0 = g * group;
     const int slot = token_slot[t];
+    const int rec = dv + 2;
     if (slot < 0) {
-        for (int i = threadIdx.x; i < group * dv; i += blockDim.x)
-            out[((size_t)t * q_heads + head0) * dv + i] = __float2bfloat16_rn(0.0f);
-        return;
+        if (splits == 1)
+            for (int i = threadIdx.x; i < group * dv; i += blockDim.x)
+                out[((size_t)t * q_heads + head0) * dv + i] = __float2bfloat16_rn(0.0f);
+        return;                       // the combining kernel writes the zeros of a row without a request
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane / LPK, li = lane % LPK;
-    const int stream = warp * (32 / LPK) + sub;
     const int pos = positions[t];
     const int lo = first_key(pos, mod);
     const int* table = block_table + (size_t)slot * max_pages;
-    const bool has_k = li * 8 < dk, has_v = li * 8 < dv;
+    int kt_first = lo / kPfN, kt_last = pos / kPfN;
+    if (splits > 1) {
+        const int per = (kt_last - kt_first + splits) / splits;
+        kt_first += split * per;
+        kt_last = min(kt_last, kt_first + per - 1);
+    }
 
-    float qf[GS][8], slope[GS];
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;                       // rows of the tile: heads of the group
+    const bool v_lo = r_lo < group, v_hi = r_hi < group;
+    const float slope_lo = (slopes != nullptr && v_lo) ? slopes[head0 + r_lo] : 0.0f;
+    const float slope_hi = (slopes != nullptr && v_hi) ? slopes[head0 + r_hi] : 0.0f;
+    const bf16* q_lo = q + ((size_t)t * q_heads + head0 + r_lo) * dk;
+    const bf16* q_hi = q + ((size_t)t * q_heads + head0 + r_hi) * dk;
+    uint32_t qa[DKP / 16][4];
 #pragma unroll
-    for (int h = 0; h < GS; ++h) {
-        slope[h] = (slopes != nullptr && h < group) ? slopes[head0 + h] : 0.0f;
+    for (int ks = 0; ks < DKP / 16; ++ks) {
+        const int c0 = ks * 16 + (lane & 3) * 2;
+        qa[ks][0] = (v_lo && c0 < dk) ? *reinterpret_cast<const uint32_t*>(q_lo + c0) : 0u;
+        qa[ks][1] = (v_hi && c0 < dk) ? *reinterpret_cast<const uint32_t*>(q_hi + c0) : 0u;
+        qa[ks][2] = (v_lo && c0 + 8 < dk) ? *reinterpret_cast<const uint32_t*>(q_lo + c0 + 8) : 0u;
+        qa[ks][3] = (v_hi && c0 + 8 < dk) ? *reinterpret_cast<const uint32_t*>(q_hi + c0 + 8) : 0u;
+    }
+    float o[DVP / 8][4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) qf[h][e] = 0.0f;
-        if (h < group && has_k) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(q + ((size_t)t * q_heads + head0 + h) * dk + li * 8);
-            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(p2[e]);
-                qf[h][2 * e] = f.x;
-                qf[h][2 * e + 1] = f.y;
+    for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const bool first = mod.sink && warp == 0 && split == 0;
+    float m_lo = first ? 0.0f : -INFINITY, m_hi = m_lo;
+    float l_lo = (first && (lane & 3) == 0) ? 1.0f : 0.0f, l_hi = l_lo;
+
+    auto issue = [&](int kt, int stage) {
+        const uint32_t ks = smem_u32(pf_smem + (size_t)stage * (kKBytes + kVBytes));
+        const uint32_t vs = ks + kKBytes;
+        constexpr int kKC = DKP / 8, kVC = DVP / 8;
+        for (int row = threadIdx.x / kKC, chunk = threadIdx.x % kKC; row < kPfN; row += kPfWarps * 32 / kKC) {
+            const int key = kt * kPfN + row;
+            const int page = (key <= pos && key >= lo) ? table[key / page_size] : -1;
+            const bool ok = page >= 0;
+            const long long page_at = ok ? (long long)page * page_stride : 0;
+            const long long in_page = (long long)g * page_size + key % page_size;
+            const bool k_ok = ok && chunk * 8 < dk;
+            cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
+            if (kKC == kVC) {
+                const bool v_ok = ok && chunk * 8 < dv;
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * dv + chunk * 8 : 0), v_ok);
             }
         }
-    }
-    float m[GS], l[GS], acc[GS][8];
-#pragma unroll
-    for (int h = 0; h < GS; ++h) {
-        const bool first = mod.sink && stream == 0;
-        m[h] = first ? 0.0f : -INFINITY;
-        l[h] = first ? 1.0f : 0.0f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
-    }
-    // the warp's lanes walk the loop together (the shuffles below take all of them); a stream whose key
-    // lies past the row's own position idles in the last round
-    for (int j0 = lo + warp * (32 / LPK); j0 <= pos; j0 += kStreams) {
-        const int j = j0 + sub;
-        const int page = j <= pos ? table[j / page_size] : -1;
-        const bool ok = page >= 0;
-        const long long base = (long long)(ok ? page : 0) * page_stride;
-        const size_t in_page = (size_t)g * page_size + (j % page_size);
-        uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
-        if (ok && has_k) kraw = *reinterpret_cast<const uint4*>(k_plane + base + in_page * dk + li * 8);
-        if (ok && has_v) vraw = *reinterpret_cast<const uint4*>(v_plane + base + in_page * dv + li * 8);
-        float kf[8], vf[8];
-        {
-            const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kraw);
-            const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vraw);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 a = __bfloat1622float2(k2[e]), b = __bfloat1622float2(v2[e]);
-                kf[2 * e] = a.x; kf[2 * e + 1] = a.y;
-                vf[2 * e] = b.x; vf[2 * e + 1] = b.y;
+        if (kKC != kVC) {
+            for (int row = threadIdx.x / kVC, chunk = threadIdx.x % kVC; row < kPfN; row += kPfWarps * 32 / kVC) {
+                const int key = kt * kPfN + row;
+                const int page = (key <= pos && key >= lo) ? table[key / page_size] : -1;
+                const bool v_ok = page >= 0 && chunk * 8 < dv;
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + key % page_size) * dv + chunk * 8 : 0), v_ok);
             }
         }
-#pragma unroll
-        for (int h = 0; h < GS; ++h) {
-            float dot = 0.0f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dot += qf[h][e] * kf[e];
-#pragma unroll
-            for (int o2 = LPK / 2; o2 > 0; o2 >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
-            if (!ok) continue;             // uniform within the key's lanes
-            const float sc = mod_score(dot, slope[h], pos - j, mod);
-            const float m_new = fmaxf(m[h], sc);
-            const float corr = expf(m[h] - m_new), p = expf(sc - m_new);
-            l[h] = l[h] * corr + p;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[h][e] = acc[h][e] * corr + p * vf[e];
-            m[h] = m_new;
+        cp_async_commit();
+    };
+
+    const int k_steps = (dk + 15) / 16, v_pairs = (dv + 15) / 16;
+    if (kt_first <= kt_last) issue(kt_first, 0);
+    for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int stage = (kt - kt_first) & 1;
+        if (kt + 1 <= kt_last) {
+            issue(kt + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
+        __syncthreads();
+        const int key0 = kt * kPfN + warp * 16;                          // this warp's 16 keys of the tile
+        if (key0 <= pos && key0 + 15 >= lo) {
+            const uint32_t ks_base = smem_u32(pf_smem + (size_t)stage * (kKBytes + kVBytes));
+            const uint32_t vs_base = ks_base + kKBytes;
+            const int mid = lane >> 3, mrow = lane & 7;
+            float s[2][4];
+            s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < DKP / 16; ++ks) {
+                if (ks < k_steps) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, ks_base + ((warp * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
+                    const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+                    mma_bf16_16816(s[0], qa[ks], b0);
+                    mma_bf16_16816(s[1], qa[ks], b1);
+                }
+            }
+            const int key_base = key0 + (lane & 3) * 2;
+            float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = key_base + nt * 8 + e;
+                    const bool seen = j <= pos && j >= lo;
+                    s[nt][e] = (seen && v_lo) ? mod_score_fast(s[nt][e], slope_lo, pos - j, mod) : -INFINITY;
+                    s[nt][2 + e] = (seen && v_hi) ? mod_score_fast(s[nt][2 + e], slope_hi, pos - j, mod) : -INFINITY;
+                    tmax_lo = fmaxf(tmax_lo, s[nt][e]);
+                    tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
+                }
+            tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
+            tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
+            tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
+            tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
+            const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
+            const float ms_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
+            const float c_lo = exp2f(m_lo - ms_lo), c_hi = exp2f(m_hi - ms_hi);
+            m_lo = mn_lo;
+            m_hi = mn_hi;
+            float sum_lo = 0.0f, sum_hi = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    s[nt][e] = exp2f(s[nt][e] - ms_lo);
+                    s[nt][2 + e] = exp2f(s[nt][2 + e] - ms_hi);
+                    sum_lo += s[nt][e];
+                    sum_hi += s[nt][2 + e];
+                }
+            l_lo = l_lo * c_lo + sum_lo;
+            l_hi = l_hi * c_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < DVP / 8; ++i) {
+                o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+            }
+            const uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                                    pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+            for (int c = 0; c < DVP / 8; c += 2) {
+                if (c / 2 < v_pairs) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vs_base + ((warp * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
+                    const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+                    mma_bf16_16816(o[c], pa, b0);
+                    mma_bf16_16816(o[c + 1], pa, b1);
+                }
+            }
+        }
+        __syncthreads();
     }
-    // streams meet: [stream][head][dv + 2]
-    const int rec = dv + 2;
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    // the warps meet: [warp][head of the group][dv + 2] floats, over the staging buffers (all reads of which are done)
+    float* meet = reinterpret_cast<float*>(pf_smem);
 #pragma unroll
-    for (int h = 0; h < GS; ++h) {
-        if (h >= group) continue;
-        float* dst = dec_smem + ((size_t)stream * group + h) * rec;
-        if (has_v) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dst[li * 8 + e] = acc[h][e];
-        }
-        if (li == 0) { dst[dv] = m[h]; dst[dv + 1] = l[h]; }
+    for (int i = 0; i < DVP / 8; ++i) {
+        const int col = i * 8 + (lane & 3) * 2;
+        if (col >= dv) continue;
+        if (v_lo) { float* d = meet + ((size_t)warp * group + r_lo) * rec; d[col] = o[i][0]; d[col + 1] = o[i][1]; }
+        if (v_hi) { float* d = meet + ((size_t)warp * group + r_hi) * rec; d[col] = o[i][2]; d[col + 1] = o[i][3]; }
+    }
+    if ((lane & 3) == 0) {
+        if (v_lo) { float* d = meet + ((size_t)warp * group + r_lo) * rec; d[dv] = m_lo; d[dv + 1] = l_lo; }
+        if (v_hi) { float* d = meet + ((size_t)warp * group + r_hi) * rec; d[dv] = m_hi; d[dv + 1] = l_hi; }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < group * dv; i += blockDim.x) {
         const int h = i / dv, e = i % dv;
         float mm = -INFINITY;
-        for (int s2 = 0; s2 < kStreams; ++s2) mm = fmaxf(mm, dec_smem[((size_t)s2 * group + h) * rec + dv]);
+#pragma unroll
+        for (int w = 0; w < kPfWarps; ++w) mm = fmaxf(mm, meet[((size_t)w * group + h) * rec + dv]);
         float total = 0.0f, v = 0.0f;
-        for (int s2 = 0; s2 < kStreams; ++s2) {
-            const float* src = dec_smem + ((size_t)s2 * group + h) * rec;
-            const float w = src[dv] == -INFINITY ? 0.0f : expf(src[dv] - mm);
-            total += src[dv + 1] * w;
-            v += src[e] * w;
+#pragma unroll
+        for (int w = 0; w < kPfWarps; ++w) {
+            const float* src = meet + ((size_t)w * group + h) * rec;
+            const float wt = src[dv] == -INFINITY ? 0.0f : exp2f(src[dv] - mm);
+            total += src[dv + 1] * wt;
+            v += src[e] * wt;
+        }
+        if (splits > 1) {
+            // [row of the grid][head][split][dv + 2]: sums, then maximum (base 2) and weight
+            float* dst = part + (((size_t)blockIdx.x * q_heads + head0 + h) * splits + split) * rec;
+            dst[e] = v;
+            if (e == 0) { dst[dv] = mm; dst[dv + 1] = total; }
+            continue;
         }
         v = total > 0.0f ? v / total : 0.0f;
         if (gate != nullptr)
@@ -571,25 +680,56 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
     }
 }
 
-template <int GS, int LPK>
+// The runs of a (row, head) added in their order, the gate applied, the result written.
+__global__ void attention_biased_combine_kernel(const float* part, const int* __restrict__ token_slot,
+                                                const int* __restrict__ rows, int q_heads, int dv, int splits,
+                                                const bf16* gate, int gate_stride, bf16* __restrict__ out) {
+    TLLM_PDL_ENTER();
+    const int t = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+    const int head = blockIdx.y, rec = dv + 2;
+    bf16* dst = out + ((size_t)t * q_heads + head) * dv;
+    if (token_slot[t] < 0) {
+        for (int e = threadIdx.x; e < dv; e += blockDim.x) dst[e] = __float2bfloat16_rn(0.0f);
+        return;
+    }
+    const float* src = part + ((size_t)blockIdx.x * q_heads + head) * splits * rec;
+    float mm = -INFINITY;
+    for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, src[s2 * rec + dv]);
+    for (int e = threadIdx.x; e < dv; e += blockDim.x) {
+        float total = 0.0f, v = 0.0f;
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float ms = src[s2 * rec + dv];
+            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+            total += src[s2 * rec + dv + 1] * w;
+            v += src[s2 * rec + e] * w;
+        }
+        v = total > 0.0f ? v / total : 0.0f;
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)head * dv + e])));
+        dst[e] = __float2bfloat16_rn(v);
+    }
+}
+
+template <int DKP, int DVP>
 static int launch_biased_decode(const void* q, const void* kp, const void* vp, long long page_stride,
                                 const int* positions, const int* token_slot, const int* rows, int n_rows,
                                 const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads,
                                 int dk, int dv, ScoreMod mod, const float* slopes, const void* gate,
-                                int gate_stride, void* out, cudaStream_t stream) {
-    const int streams = kDecWarps * (32 / LPK);
-    const size_t smem = (size_t)streams * (q_heads / kv_heads) * (dv + 2) * sizeof(float);
+                                int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
+    const size_t smem = (size_t)2 * kPfN * ((DKP + kPfPad) + (DVP + kPfPad)) * 2;      // also holds the warps' meeting
     static OncePerDevice configured;
     if (configured.first()) {
-        cudaError_t e = cudaFuncSetAttribute(attention_biased_decode_kernel<GS, LPK>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attention_biased_decode_kernel<DKP, DVP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { set_error("attention_biased_decode: %s", cudaGetErrorString(e)); return (int)e; }
         configured.done();
     }
-    launch_pdl(kPdlAttention, attention_biased_decode_kernel<GS, LPK>, dim3(n_rows, kv_heads), dim3(kDecWarps * 32),
+    launch_pdl(kPdlAttention, attention_biased_decode_kernel<DKP, DVP>, dim3(n_rows, kv_heads, splits), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, positions, token_slot,
                rows, block_table, max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
-               gate_stride, (bf16*)out);
+               gate_stride, splits, part, (bf16*)out);
+    if (splits > 1)
+        launch_pdl(kPdlCombine, attention_biased_combine_kernel, dim3(n_rows, q_heads), dim3(dv >= 128 ? 128 : 64), 0, stream,
+                   (const float*)part, token_slot, rows, q_heads, dv, splits, (const bf16*)gate, gate_stride, (bf16*)out);
     return finish_launch("attention_biased_decode");
 }
 
@@ -649,7 +789,7 @@ int tllm_attention_biased_general(
 
 // Whether the two bfloat16 kernels below take these sizes (else the general kernel serves).
 int tllm_attention_biased_fast_ok(int q_heads, int kv_heads, int dk, int dv) {
-    return q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 8 &&
+    return q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16 &&
            dk % 8 == 0 && dv % 8 == 0 && dk > 0 && dv > 0 && dk <= 128 && dv <= 128;
 }
 
@@ -673,26 +813,24 @@ int tllm_attention_biased_prefill(
 #undef PF
 }
 
-// rows: indices of the one-token rows (null: rows 0 .. n_rows - 1).
+// rows: indices of the one-token rows (null: rows 0 .. n_rows - 1).  splits: runs of keys per (row,
+// key/value head), each a block; with more than one, `part` holds n_rows * q_heads * splits * (dv + 2) floats.
 int tllm_attention_biased_decode(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* rows, int n_rows, const int* block_table, int max_pages, int page_size,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const void* gate, int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_decode: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_rows >= 0 && kv_heads <= 65535, "attention_biased_decode: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_decode: negative constant");
+    TLLM_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || part != nullptr), "attention_biased_decode: %d runs of keys", splits);
     if (n_rows == 0) return 0;
     const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
-    const int group = q_heads / kv_heads;
-    const int wide = dk > dv ? dk : dv;
-#define DEC(G, L) launch_biased_decode<G, L>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
-                                             max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream)
-#define DEC_G(L) (group <= 1 ? DEC(1, L) : group <= 2 ? DEC(2, L) : group <= 4 ? DEC(4, L) : DEC(8, L))
-    if (wide <= 32) return DEC_G(4);
-    if (wide <= 64) return DEC_G(8);
-    return DEC_G(16);
-#undef DEC_G
+#define DEC(A, B) launch_biased_decode<A, B>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
+                                             max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride,    \
+                                             splits, part, out, stream)
+    if (dk <= 64) return dv <= 64 ? DEC(64, 64) : DEC(64, 128);
+    return dv <= 64 ? DEC(128, 64) : DEC(128, 128);
 #undef DEC
 }
 

@@ -163,11 +163,24 @@ __device__ __forceinline__ void store_row32(bf16* row_ptr, int col0, int cols, c
 // owns 256 rows, both accumulators belong to one tile, every slab of W fetched from L2 feeds
 // twice as many MMAs (32 KB of shared-memory fill per 128 x 256 x 64 instead of 48 KB), three
 // stages of 64 KB; the epilogue is not overlapped.
+// Grouped form (a mixture of experts): x holds the rows of every expert one after the other, w the
+// experts' matrices stacked ([experts * w_rows, K]), and a row tile is an entry of device-side lists made
+// by the step's plan: its expert and its first row, wherever that falls; rows at and past the expert's
+// last (`offsets[expert + 1]`) are computed along and not written.  How many entries there are is read
+// from the device too (`n_tiles`); `tile_row0 == nullptr` means the plain form.
+struct GroupedTiles {
+    const int* tile_expert;
+    const int* tile_row0;
+    const int* n_tiles;
+    const int* offsets;
+    int w_rows;
+};
+
 template <bool SWIGLU, int MT, int ACT>
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ y, int M, int N, int K, int half_n, int interleaved, int tiles_m,
-                    int tiles_n, int* __restrict__ error_word) {
+                    int tiles_n, int* __restrict__ error_word, const GroupedTiles grouped) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[4], empty_bar[4], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -182,6 +195,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* stage_out = tiles + (size_t)kStages * kStageBytes + (size_t)(warp & 3) * 32 * kOutRowBytes;
     const int k_blocks = (K + kBK - 1) / kBK;
+    if (grouped.tile_row0 != nullptr) tiles_m = *grouped.n_tiles;
     const int total_tiles = tiles_m * tiles_n;
     const int out_cols = SWIGLU ? half_n : N;
     constexpr int kColTile = SWIGLU ? 128 : kBN;
@@ -217,6 +231,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             int it = 0;                               // k-blocks issued so far, over all tiles
             for (int t = blockIdx.x; t < total_tiles && !*aborted; t += gridDim.x) {
                 const int tile_m = t % tiles_m, tile_n = t / tiles_m;
+                int a_row = tile_m * kRows, w_row = 0;
+                if (grouped.tile_row0 != nullptr) {
+                    a_row = grouped.tile_row0[tile_m];
+                    w_row = grouped.tile_expert[tile_m] * grouped.w_rows;
+                }
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
                     if (it >= kStages && !mbar_wait(&empty_bar[s], ((it / kStages) - 1) & 1)) {
@@ -227,13 +246,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     unsigned char* a_dst = tiles + (size_t)s * kStageBytes;
                     unsigned char* b_dst = a_dst + kStageABytes;
                     mbar_expect_tx(&full_bar[s], kStageBytes);
-                    tma_load_2d(a_dst, &map_x, kb * kBK, tile_m * kRows, &full_bar[s]);
+                    tma_load_2d(a_dst, &map_x, kb * kBK, a_row, &full_bar[s]);
                     if (SWIGLU && !interleaved) {
-                        tma_load_2d(b_dst, &map_w, kb * kBK, tile_n * 128, &full_bar[s]);
-                        tma_load_2d(b_dst + kStageBBytes / 2, &map_w, kb * kBK, half_n + tile_n * 128, &full_bar[s]);
+                        tma_load_2d(b_dst, &map_w, kb * kBK, w_row + tile_n * 128, &full_bar[s]);
+                        tma_load_2d(b_dst + kStageBBytes / 2, &map_w, kb * kBK, w_row + half_n + tile_n * 128, &full_bar[s]);
                     } else {
-                        tma_load_2d(b_dst, &map_w, kb * kBK, tile_n * kBN, &full_bar[s]);
-                        tma_load_2d(b_dst + kStageBBytes / 2, &map_w, kb * kBK, tile_n * kBN + 128, &full_bar[s]);
+                        tma_load_2d(b_dst, &map_w, kb * kBK, w_row + tile_n * kBN, &full_bar[s]);
+                        tma_load_2d(b_dst + kStageBBytes / 2, &map_w, kb * kBK, w_row + tile_n * kBN + 128, &full_bar[s]);
                     }
                 }
             }
@@ -288,6 +307,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
             const int buf = local % kNumBuf;
             const int tile_m = t % tiles_m, tile_n = t / tiles_m;
+            int row_base = tile_m * kRows, row_end = M;
+            if (grouped.tile_row0 != nullptr) {
+                row_base = grouped.tile_row0[tile_m];
+                row_end = grouped.offsets[grouped.tile_expert[tile_m] + 1];
+            }
             const bool ready = mbar_wait(&acc_full[buf], (local / kNumBuf) & 1);
             if (!ready) {
                 if (lane == 0) atomicExch(error_word, 3);
@@ -297,7 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
-                const int row0 = tile_m * kRows + mt * kBM + quad * 32;          // first row of this warp
+                const int row0 = row_base + mt * kBM + quad * 32;                // first row of this warp
                 const uint32_t lane_addr = tmem_base + (buf + mt) * kBN + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
                 for (int c = 0; c < kColTile; c += 64) {                          // 64 output columns at a time
@@ -352,7 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     for (int j = 0; j < 8; ++j) {
                         const int piece = lane + 32 * j, r = piece >> 3, p16 = piece & 7;
                         const int row = row0 + r, col = col0 + p16 * 8;
-                        if (row < M && col < out_cols) {
+                        if (row < row_end && col < out_cols) {
                             const uint4 val = *reinterpret_cast<const uint4*>(stage_out + r * kOutRowBytes + p16 * 16);
                             bf16* dst = y + (size_t)row * out_cols + col;
                             if (col + 8 <= out_cols && (out_cols % 8) == 0) {
@@ -423,7 +447,9 @@ static int sm_count() {
 
 template <bool SWIGLU, int MT, int ACT = kActSilu>
 static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int M, int N, int K, int half_n,
-                          int interleaved, int* error_word, cudaStream_t stream) {
+                          int interleaved, int* error_word, cudaStream_t stream,
+                          const GroupedTiles grouped = GroupedTiles{nullptr, nullptr, nullptr, nullptr, 0},
+                          int grouped_max_tiles = 0) {
     const size_t smem = (size_t)(MT == 1 ? 4 : 3) * (kBM * MT * kBK * 2 + kStageBBytes) + 1024 + 4 * 32 * (64 * 2 + 16);
     static OncePerDevice configured;
     if (configured.first()) {
@@ -434,11 +460,12 @@ static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y,
     }
     const int out_cols = SWIGLU ? half_n : N;
     const int col_tile = SWIGLU ? 128 : kBN;
-    const int tiles_n = (out_cols + col_tile - 1) / col_tile, tiles_m = (M + kBM * MT - 1) / (kBM * MT);
+    const int tiles_n = (out_cols + col_tile - 1) / col_tile;
+    const int tiles_m = grouped.tile_row0 != nullptr ? grouped_max_tiles : (M + kBM * MT - 1) / (kBM * MT);
     const int total = tiles_m * tiles_n;
     const int grid = total < sm_count() ? total : sm_count();
     gemm_tcgen05_kernel<SWIGLU, MT, ACT><<<grid, kGemmThreads, smem, stream>>>(mx, mw, (bf16*)y, M, N, K, half_n, interleaved,
-                                                                      tiles_m, tiles_n, error_word);
+                                                                      tiles_m, tiles_n, error_word, grouped);
     return finish_launch("gemm_tcgen05");
 }
 
@@ -476,4 +503,30 @@ extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, i
                     : launch_tcgen05<true, 1>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream);
     return tall ? launch_tcgen05<false, 2>(mx, mw, y, M, N, K, 0, 0, error_word, stream)
                 : launch_tcgen05<false, 1>(mx, mw, y, M, N, K, 0, 0, error_word, stream);
+}
+
+// The grouped form: x [rows, K] holds the experts' rows one after the other, w is [experts][n][K], and
+// the row tiles of 128 are the plan's lists (device memory; at most max_tiles entries).  flags as in
+// tllm_gemm_tcgen05 (bit 1 with bit 4: gate and up rows interleaved by eight, y is [rows, n / 2]).
+extern "C" int tllm_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int rows, int n, int K, int experts,
+                                         int flags, const int* tile_expert, const int* tile_row0, const int* n_tiles,
+                                         const int* offsets, int max_tiles, int* error_word, cudaStream_t stream) {
+    TLLM_REQUIRE(rows > 0 && n > 0 && K > 0 && experts > 0 && max_tiles > 0, "gemm_tcgen05_grouped: bad sizes");
+    TLLM_REQUIRE(K % 8 == 0, "gemm_tcgen05_grouped: K = %d is no multiple of 8", K);
+    const bool gated = flags & 1;
+    TLLM_REQUIRE(!gated || ((flags & 4) && n % 16 == 0), "gemm_tcgen05_grouped: gate and up rows interleaved by eight, n = %d", n);
+    TLLM_REQUIRE((gated ? n / 2 : n) % 8 == 0, "gemm_tcgen05_grouped: rows of y must be whole 16-byte pieces");
+    TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0,
+                 "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+    TLLM_REQUIRE(error_word && tile_expert && tile_row0 && n_tiles && offsets, "gemm_tcgen05_grouped: missing list");
+    CUtensorMap mx, mw;
+    TLLM_REQUIRE(make_map(&mx, x, rows, K, kBM) && make_map(&mw, w, (long long)experts * n, K, 128),
+                 "gemm_tcgen05_grouped: cuTensorMapEncodeTiled failed or is not available");
+    const GroupedTiles grouped{tile_expert, tile_row0, n_tiles, offsets, n};
+    const int act = flags >> 8;
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tcgen05_grouped: unknown activation %d", act);
+    if (gated && act == kActGeluTanh)
+        return launch_tcgen05<true, 1, kActGeluTanh>(mx, mw, y, rows, n, K, n / 2, 1, error_word, stream, grouped, max_tiles);
+    if (gated) return launch_tcgen05<true, 1>(mx, mw, y, rows, n, K, n / 2, 1, error_word, stream, grouped, max_tiles);
+    return launch_tcgen05<false, 1>(mx, mw, y, rows, n, K, 0, 0, error_word, stream, grouped, max_tiles);
 }

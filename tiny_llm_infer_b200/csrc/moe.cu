@@ -5,7 +5,8 @@
 //   route    z [T, E] float32 router logits -> the `top` experts with the largest z per token
 //            (lowest index first on ties) and their weights, sigmoid(z) or softmax over the chosen;
 //   plan     counting sort of the T * top assignments by expert: offsets per expert, the row every
-//            assignment gets, and the list of (expert, first row) tiles of kTileRows rows;
+//            assignment gets, and the list of (expert, first row) tiles of the rows (64 for the mma.sync
+//            products of this file, 128 for the grouped tcgen05 product);
 //   products C[row] = A[row] . W_e^T for the expert e that owns the row.  The first product can
 //            gather its rows from the tokens (scaled by the assignment's weight, for routers whose
 //            weight multiplies the expert's input) and apply act(gate) * up in its epilogue; bfloat16
@@ -60,8 +61,8 @@ __global__ void moe_route_kernel(const float* z, int tokens, int experts, int to
 // ---------------------------------------------------------------- plan
 // One block.  ints: offsets [E + 1] | n_tiles [1] | row_of [n] | src_of [n] | expert_of_row [n] |
 // tile_expert [max tiles] | tile_row0 [max tiles].
-__global__ void moe_plan_kernel(const int* ids, int n, int experts, int* offsets, int* n_tiles, int* row_of,
-                                int* src_of, int* expert_of_row, int* tile_expert, int* tile_row0) {
+__global__ void moe_plan_kernel(const int* ids, int n, int experts, int tile_rows, int* offsets, int* n_tiles,
+                                int* row_of, int* src_of, int* expert_of_row, int* tile_expert, int* tile_row0) {
     extern __shared__ int plan_smem[];
     TLLM_PDL_ENTER();
     int* count = plan_smem;                 // [E]
@@ -74,7 +75,7 @@ __global__ void moe_plan_kernel(const int* ids, int n, int experts, int* offsets
         int at = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
             offsets[e] = cursor[e] = at;
-            for (int r = at; r < at + count[e]; r += kTileRows) { tile_expert[tiles] = e; tile_row0[tiles] = r; ++tiles; }
+            for (int r = at; r < at + count[e]; r += tile_rows) { tile_expert[tiles] = e; tile_row0[tiles] = r; ++tiles; }
             at += count[e];
         }
         offsets[experts] = at;
@@ -105,6 +106,13 @@ __device__ __forceinline__ uint4 scale8(uint4 raw, float w) {
     return raw;
 }
 
+// Row of an expert's gate|up matrix that holds output column `col`'s gate (or up) weights: stacked
+// ([gate; up]) or interleaved by eight (eight gate rows, their eight up rows, and so on).
+__device__ __forceinline__ int gate_up_row(int col, bool up, int n, int interleaved) {
+    if (interleaved) return 16 * (col >> 3) + (col & 7) + (up ? 8 : 0);
+    return up ? n + col : col;
+}
+
 // GATED: a block's 64 weight rows are, per warp column of 32, sixteen gate rows and the sixteen up rows
 // that belong to them; the block writes 32 columns of act(gate) * up in bfloat16.  Otherwise 64 columns
 // of the plain product in float32.
@@ -112,7 +120,7 @@ template <bool GATED, bool GATHER>
 __global__ void __launch_bounds__(kGThreads)
 moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* weight_of, int top,
                        const bf16* W, long long w_stride, const int* tile_expert, const int* tile_row0,
-                       const int* n_tiles, const int* offsets, int N, int K, int act, void* C) {
+                       const int* n_tiles, const int* offsets, int N, int K, int act, int interleaved, void* C) {
     __shared__ __align__(16) bf16 As[2][kGM][kGK + kGPad];
     __shared__ __align__(16) bf16 Bs[2][kGN][kGK + kGPad];
     TLLM_PDL_ENTER();
@@ -150,7 +158,7 @@ moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* w
         if (GATED) {
             const int half = r >> 5, j = r & 31;
             const int col = n0 + half * 16 + (j & 15);
-            wrow = col < N ? (j < 16 ? col : N + col) : -1;
+            wrow = col < N ? gate_up_row(col, j >= 16, N, interleaved) : -1;
         } else {
             wrow = n0 + r < N ? n0 + r : -1;
         }
@@ -246,7 +254,7 @@ moe_grouped_mma_kernel(const bf16* A, int lda, const int* src_of, const float* w
 template <typename TA, bool GATED, bool GATHER>
 __global__ void moe_grouped_plain_kernel(const TA* A, int lda, const int* src_of, const float* weight_of, int top,
                                          const TA* W, long long w_stride, const int* expert_of_row, int rows,
-                                         int N, int K, int act, void* C) {
+                                         int N, int K, int act, int interleaved, void* C) {
     TLLM_PDL_ENTER();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * N) return;
@@ -261,10 +269,10 @@ __global__ void moe_grouped_plain_kernel(const TA* A, int lda, const int* src_of
         a = A + (size_t)r * lda;
     }
     const TA* We = W + (long long)expert_of_row[r] * w_stride;
-    const TA* wg = We + (size_t)n * K;
+    const TA* wg = We + (size_t)(GATED ? gate_up_row(n, false, N, interleaved) : n) * K;
     float g = 0.0f, u = 0.0f;
     if (GATED) {
-        const TA* wu = We + (size_t)(N + n) * K;
+        const TA* wu = We + (size_t)gate_up_row(n, true, N, interleaved) * K;
         for (int k = 0; k < K; ++k) {
             const float x = to_f32<TA>(from_f32<TA>(to_f32<TA>(a[k]) * w));     // the rounding of the scaled row
             g += x * to_f32<TA>(wg[k]);
@@ -277,9 +285,27 @@ __global__ void moe_grouped_plain_kernel(const TA* A, int lda, const int* src_of
     }
 }
 
+// ---------------------------------------------------------------- gather
+// xs[row] = x[token of the row] (* the assignment's weight): the experts' rows one after the other, for a
+// product that reads its rows by TMA.  16 bytes per thread.
+__global__ void moe_gather_kernel(const bf16* x, const int* src_of, const float* weight_of, int top, bf16* xs,
+                                  int width, size_t total_chunks) {
+    TLLM_PDL_ENTER();
+    const int per_row = width >> 3;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total_chunks; idx += stride) {
+        const size_t r = idx / per_row, c = idx - r * per_row;
+        const int a = src_of[r];
+        uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(a / top) * width + c * 8);
+        if (weight_of != nullptr) raw = scale8(raw, weight_of[a]);
+        *reinterpret_cast<uint4*>(xs + r * width + c * 8) = raw;
+    }
+}
+
 // ---------------------------------------------------------------- combine
-template <typename T>
-__global__ void moe_combine_kernel(const float* y, const int* row_of, const float* weight_of, int top,
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* y, const int* row_of, const float* weight_of, int top,
                                    const T* shared, T* out, int width, size_t total) {
     TLLM_PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -288,7 +314,7 @@ __global__ void moe_combine_kernel(const float* y, const int* row_of, const floa
         const size_t t = idx / width, i = idx - t * width;
         float v = shared != nullptr ? to_f32<T>(shared[idx]) : 0.0f;
         for (int k = 0; k < top; ++k) {
-            const float yv = y[(size_t)row_of[t * top + k] * width + i];
+            const float yv = to_f32<TY>(y[(size_t)row_of[t * top + k] * width + i]);
             v += weight_of != nullptr ? weight_of[t * top + k] * yv : yv;
         }
         out[idx] = from_f32<T>(v);
@@ -314,11 +340,11 @@ int tllm_moe_route(const float* z, int tokens, int experts, int top, int softmax
     return finish_launch("moe_route");
 }
 
-int tllm_moe_plan(const int* ids, int n, int experts, int* offsets, int* n_tiles, int* row_of, int* src_of,
-                  int* expert_of_row, int* tile_expert, int* tile_row0, cudaStream_t stream) {
-    TLLM_REQUIRE(n > 0 && experts > 0 && experts <= 4096, "moe_plan: bad sizes");
+int tllm_moe_plan(const int* ids, int n, int experts, int tile_rows, int* offsets, int* n_tiles, int* row_of,
+                  int* src_of, int* expert_of_row, int* tile_expert, int* tile_row0, cudaStream_t stream) {
+    TLLM_REQUIRE(n > 0 && experts > 0 && experts <= 4096 && tile_rows > 0, "moe_plan: bad sizes");
     launch_pdl(kPdlOther, moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), stream,
-               ids, n, experts, offsets, n_tiles, row_of, src_of, expert_of_row, tile_expert, tile_row0);
+               ids, n, experts, tile_rows, offsets, n_tiles, row_of, src_of, expert_of_row, tile_expert, tile_row0);
     return finish_launch("moe_plan");
 }
 
@@ -329,7 +355,8 @@ int tllm_moe_plan(const int* ids, int n, int experts, int* offsets, int* n_tiles
 int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* weight_of, int top, const void* W,
                      long long w_stride, const int* tile_expert, const int* tile_row0, const int* n_tiles,
                      const int* offsets, const int* expert_of_row, int rows, int max_tiles, int N, int K,
-                     int dtype, int gated, int gather, int act, void* C, cudaStream_t stream) {
+                     int dtype, int gated, int gather, int act, int interleaved, void* C, cudaStream_t stream) {
+    TLLM_REQUIRE(!interleaved || (gated && N % 8 == 0), "moe_grouped: interleaved gate and up rows need N %% 8 == 0");
     TLLM_REQUIRE(rows >= 0 && N > 0 && K > 0 && max_tiles > 0, "moe_grouped: bad sizes");
     TLLM_REQUIRE(dtype == kBF16 || dtype == kF32, "moe_grouped: unknown dtype %d", dtype);
     TLLM_REQUIRE(max_tiles <= 65535, "moe_grouped: %d row tiles exceed 65535", max_tiles);
@@ -340,7 +367,7 @@ int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* wei
         const dim3 grid((N + cols - 1) / cols, max_tiles), block(kGThreads);
 #define MMA(G, H)                                                                                              \
     launch_pdl(kPdlOther, moe_grouped_mma_kernel<G, H>, grid, block, 0, stream, (const bf16*)A, lda, src_of,    \
-               weight_of, top, (const bf16*)W, w_stride, tile_expert, tile_row0, n_tiles, offsets, N, K, act, C)
+               weight_of, top, (const bf16*)W, w_stride, tile_expert, tile_row0, n_tiles, offsets, N, K, act, interleaved, C)
         if (gated && gather) MMA(true, true);
         else if (gated) MMA(true, false);
         else if (gather) MMA(false, true);
@@ -352,7 +379,7 @@ int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* wei
     const dim3 grid((unsigned)((total + 255) / 256)), block(256);
 #define PLAIN(T, G, H)                                                                                          \
     launch_pdl(kPdlOther, moe_grouped_plain_kernel<T, G, H>, grid, block, 0, stream, (const T*)A, lda, src_of,  \
-               weight_of, top, (const T*)W, w_stride, expert_of_row, rows, N, K, act, C)
+               weight_of, top, (const T*)W, w_stride, expert_of_row, rows, N, K, act, interleaved, C)
     if (dtype == kBF16) {
         if (gated && gather) PLAIN(bf16, true, true);
         else if (gated) PLAIN(bf16, true, false);
@@ -368,7 +395,19 @@ int tllm_moe_grouped(const void* A, int lda, const int* src_of, const float* wei
     return finish_launch("moe_grouped");
 }
 
-int tllm_moe_combine(const float* y, const int* row_of, const float* weight_of, int top, const void* shared,
+// y_dtype: float32 rows, or rows in the storage type (the grouped tcgen05 product writes bfloat16).
+int tllm_moe_gather(const void* x, const int* src_of, const float* weight_of, int top, void* xs, int rows, int width,
+                    cudaStream_t stream) {
+    TLLM_REQUIRE(rows >= 0 && width > 0 && width % 8 == 0 && top > 0, "moe_gather: bad sizes");
+    const size_t chunks = (size_t)rows * (width / 8);
+    if (chunks == 0) return 0;
+    size_t g = (chunks + 255) / 256;
+    launch_pdl(kPdlOther, moe_gather_kernel, dim3((unsigned)(g > 148 * 16 ? 148 * 16 : g)), dim3(256), 0, stream,
+               (const bf16*)x, src_of, weight_of, top, (bf16*)xs, width, chunks);
+    return finish_launch("moe_gather");
+}
+
+int tllm_moe_combine(const void* y, int y_dtype, const int* row_of, const float* weight_of, int top, const void* shared,
                      void* out, int dtype, int tokens, int width, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && width > 0 && top > 0, "moe_combine: bad sizes");
     const size_t total = (size_t)tokens * width;
@@ -376,14 +415,17 @@ int tllm_moe_combine(const float* y, const int* row_of, const float* weight_of, 
     const int block = 256;
     size_t g = (total + block - 1) / block;
     const int grid = (int)(g > 148 * 16 ? 148 * 16 : g);
-    if (dtype == kBF16)
-        launch_pdl(kPdlOther, moe_combine_kernel<bf16>, dim3(grid), dim3(block), 0, stream, y, row_of, weight_of, top,
+    if (dtype == kBF16 && y_dtype == kBF16)
+        launch_pdl(kPdlOther, moe_combine_kernel<bf16, bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)y, row_of, weight_of, top,
                    (const bf16*)shared, (bf16*)out, width, total);
-    else if (dtype == kF32)
-        launch_pdl(kPdlOther, moe_combine_kernel<float>, dim3(grid), dim3(block), 0, stream, y, row_of, weight_of, top,
+    else if (dtype == kBF16 && y_dtype == kF32)
+        launch_pdl(kPdlOther, moe_combine_kernel<bf16, float>, dim3(grid), dim3(block), 0, stream, (const float*)y, row_of, weight_of, top,
+                   (const bf16*)shared, (bf16*)out, width, total);
+    else if (dtype == kF32 && y_dtype == kF32)
+        launch_pdl(kPdlOther, moe_combine_kernel<float, float>, dim3(grid), dim3(block), 0, stream, (const float*)y, row_of, weight_of, top,
                    (const float*)shared, (float*)out, width, total);
     else
-        TLLM_REQUIRE(false, "moe_combine: unknown dtype %d", dtype);
+        TLLM_REQUIRE(false, "moe_combine: unknown dtypes %d, %d", dtype, y_dtype);
     return finish_launch("moe_combine");
 }
 

@@ -70,12 +70,14 @@ def _declare(h) -> None:
         "tllm_attention_biased_prefill": [vp, vp, vp, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
                                           f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
         "tllm_attention_biased_decode": [vp, vp, vp, i64, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                         f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+                                         f32, f32, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp],
         "tllm_moe_route": [vp, i32, i32, i32, i32, vp, vp, vp],
-        "tllm_moe_plan": [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
+        "tllm_moe_plan": [vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
         "tllm_moe_grouped": [vp, i32, vp, vp, i32, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
-                             i32, i32, vp, vp],
-        "tllm_moe_combine": [vp, vp, vp, i32, vp, vp, i32, i32, i32, vp],
+                             i32, i32, i32, vp, vp],
+        "tllm_moe_gather": [vp, vp, vp, i32, vp, i32, i32, vp],
+        "tllm_moe_combine": [vp, i32, vp, vp, i32, vp, vp, i32, i32, i32, vp],
+        "tllm_gemm_tcgen05_grouped": [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
         "tllm_add_rmsnorm": [vp, vp, vp, i32, f32, vp, i32, vp, i32, i32, vp],
         "tllm_swiglu": [vp, vp, i32, i32, i32, i32, i32, vp],
         "tllm_cast": [vp, i32, vp, i32, i64, vp],
@@ -598,6 +600,13 @@ def _plane(plane: torch.Tensor):
 BIASED_FAST = True       # False: every row takes the general kernel (for comparisons)
 
 
+def biased_decode_splits(rows: int, kv_heads: int, reach: int) -> int:
+    """Runs of keys per (row, key/value head) of ``attention_biased``'s one-token kernel: enough blocks
+    for two per multiprocessor, each run with at least 256 keys of the ``reach`` a row can see."""
+    want = -(-2 * SM_COUNT // max(rows * kv_heads, 1))
+    return max(1, min(want, reach // 256, 64))
+
+
 def qkv_unit_store(proj: torch.Tensor, q_out: torch.Tensor, positions, token_slot, block_table,
                    k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], page_size: int,
                    q_heads: int, kv_heads: int, dk: int, dv: int, eps: Optional[float],
@@ -645,16 +654,23 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
     if slopes is not None:
         assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
     gate_ptr = None if gate is None else gate.data_ptr()
-    consts = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
-              gate_ptr, gate_stride, _p(out), _stream())
+    mods = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
+            gate_ptr, gate_stride)
+    consts = mods + (_p(out), _stream())
     if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
             and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 \
             and lib().tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv):
         # one-token rows: keys read once per group of query heads; longer portions: tensor-core tiles
         if ctx.n_dec:
+            reach = min(v for v in (chunk, window, ctx.max_context or 1 << 30) if v)
+            splits = biased_decode_splits(ctx.n_dec, kv_heads, reach)
+            part = None
+            if splits > 1:
+                part = workspace(q.device, ctx.n_dec * q_heads * splits * (dv + 2))
             _check(lib().tllm_attention_biased_decode(
                 _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(ctx.dec_rows), ctx.n_dec, _p(block_table),
-                block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *consts), "attention_biased_decode")
+                block_table.shape[1], page_size, q_heads, kv_heads, dk, dv, *mods, splits, _p(part), _p(out), _stream()),
+                "attention_biased_decode", kernels=2 if splits > 1 else 1)
         if ctx.n_tiles:
             _check(lib().tllm_attention_biased_prefill(
                 _p(q), kp, vp, stride, _p(ctx.seg_info), _p(ctx.pf_tiles), ctx.n_tiles, _p(block_table),
@@ -687,12 +703,14 @@ def moe_route(z: torch.Tensor, top: int, softmax_weights: bool = False):
 
 
 class MoePlan:
-    """Device-side lists that sort a step's (token, choice) assignments by expert."""
+    """Device-side lists that sort a step's (token, choice) assignments by expert, with the rows cut
+    into tiles of ``tile_rows`` per expert."""
 
-    def __init__(self, ids: torch.Tensor, experts: int):
+    def __init__(self, ids: torch.Tensor, experts: int, tile_rows: Optional[int] = None):
         n = ids.numel()
         self.n, self.experts = n, experts
-        self.max_tiles = n // moe_tile_rows() + experts
+        self.tile_rows = tile_rows or moe_tile_rows()
+        self.max_tiles = n // self.tile_rows + experts
         ints = torch.empty(experts + 2 + 3 * n + 2 * self.max_tiles, dtype=torch.int32, device=ids.device)
         at = 0
 
@@ -704,37 +722,67 @@ class MoePlan:
         self.offsets, self.n_tiles = take(experts + 1), take(1)
         self.row_of, self.src_of, self.expert_of_row = take(n), take(n), take(n)
         self.tile_expert, self.tile_row0 = take(self.max_tiles), take(self.max_tiles)
-        _check(lib().tllm_moe_plan(_p(ids), n, experts, _p(self.offsets), _p(self.n_tiles), _p(self.row_of),
-                                   _p(self.src_of), _p(self.expert_of_row), _p(self.tile_expert),
+        _check(lib().tllm_moe_plan(_p(ids), n, experts, self.tile_rows, _p(self.offsets), _p(self.n_tiles),
+                                   _p(self.row_of), _p(self.src_of), _p(self.expert_of_row), _p(self.tile_expert),
                                    _p(self.tile_row0), _stream()), "moe_plan")
 
 
+MOE_TCGEN05_ROWS = 1024     # from this many (token, choice) rows on the experts' products run on tcgen05
+MOE_TCGEN05_TILE = 128
+
+
+def moe_tcgen05_pays(rows: int, experts: int, n: int, k: int, dtype) -> bool:
+    """Whether the experts' products of a step take the grouped tcgen05 kernel: bfloat16, whole 16-byte
+    pieces, and enough rows that an expert's tile of 128 is on average at least a quarter full."""
+    return (dtype == torch.bfloat16 and rows >= MOE_TCGEN05_ROWS and rows >= 32 * experts
+            and k % 8 == 0 and n % 8 == 0)
+
+
 def moe_grouped(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, top: int, gated: bool, gather: bool,
-                weights: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
-    """Per row r of the plan, A[r] . W[expert of r]^T.  ``w`` is [E, N (or 2 N: gate rows, then up rows), K].
-    ``gather``: ``a`` is [tokens, K] and a row reads its token, times ``weights`` [tokens, top] if given.
-    ``gated``: the result is act(gate) * up [rows, N] in the storage type, else [rows, N] float32."""
+                weights: Optional[torch.Tensor] = None, act: str = "silu", interleaved: bool = False,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Per row r of the plan, A[r] . W[expert of r]^T.  ``w`` is [E, N (or 2 N: gate rows, then up rows, or
+    ``interleaved`` by eight), K].  ``gather``: ``a`` is [tokens, K] and a row reads its token, times ``weights``
+    [tokens, top] if given.  ``gated``: the result is act(gate) * up [rows, N] in the storage type, else
+    [rows, N] float32.  A plan cut into tiles of 128 rows goes to the grouped tcgen05 product (bfloat16 in and
+    out; the gathered rows are laid out by a kernel of their own first)."""
     _cuda(a, w, weights)
     experts, n_total, k = w.shape
     assert a.shape[1] == k and a.dtype == w.dtype and experts == plan.experts
     n = n_total // 2 if gated else n_total
+    if plan.tile_rows == MOE_TCGEN05_TILE:
+        assert a.dtype == torch.bfloat16 and (interleaved or not gated)
+        if gather:
+            xs = torch.empty((plan.n, k), dtype=a.dtype, device=a.device)
+            _check(lib().tllm_moe_gather(_p(a), _p(plan.src_of), _p(weights), top, _p(xs), plan.n, k, _stream()),
+                   "moe_gather")
+            a = xs
+        out = torch.empty((plan.n, n), dtype=torch.bfloat16, device=a.device)
+        global tcgen05_calls
+        tcgen05_calls += 1
+        flags = (1 | 4 | (ACTIVATIONS[act] << 8)) if gated else 0
+        _check(lib().tllm_gemm_tcgen05_grouped(
+            _p(a), _p(w), _p(out), plan.n, n_total, k, experts, flags, _p(plan.tile_expert), _p(plan.tile_row0),
+            _p(plan.n_tiles), _p(plan.offsets), plan.max_tiles, _p(error_word(a.device)), _stream()),
+            "gemm_tcgen05_grouped")
+        return out
     out = torch.empty((plan.n, n), dtype=a.dtype if gated else torch.float32, device=a.device)
     _check(lib().tllm_moe_grouped(
         _p(a), a.stride(0), _p(plan.src_of), _p(weights), top, _p(w), w.stride(0), _p(plan.tile_expert),
         _p(plan.tile_row0), _p(plan.n_tiles), _p(plan.offsets), _p(plan.expert_of_row), plan.n, plan.max_tiles,
-        n, k, _dt(a), int(gated), int(gather), ACTIVATIONS[act], _p(out), _stream()), "moe_grouped")
+        n, k, _dt(a), int(gated), int(gather), ACTIVATIONS[act], int(interleaved), _p(out), _stream()), "moe_grouped")
     return out
 
 
 def moe_combine(y: torch.Tensor, plan: MoePlan, top: int, shared: Optional[torch.Tensor], dtype: torch.dtype,
                 weights: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = shared[t] + sum_k (weights[t, k] *) y[row of (t, k)], float32 sums, stored as ``dtype``."""
+    """out[t] = shared[t] + sum_k (weights[t, k] *) y[row of (t, k)], float32 sums, stored as ``dtype``;
+    ``y`` float32 or in the storage type."""
     _cuda(y, shared, weights)
-    assert y.dtype == torch.float32
     tokens, width = plan.n // top, y.shape[1]
     out = torch.empty((tokens, width), dtype=dtype, device=y.device)
     if shared is not None:
         assert shared.dtype == dtype and tuple(shared.shape) == (tokens, width)
-    _check(lib().tllm_moe_combine(_p(y), _p(plan.row_of), _p(weights), top, _p(shared), _p(out), _DT[dtype],
+    _check(lib().tllm_moe_combine(_p(y), _dt(y), _p(plan.row_of), _p(weights), top, _p(shared), _p(out), _DT[dtype],
                                   tokens, width, _stream()), "moe_combine")
     return out

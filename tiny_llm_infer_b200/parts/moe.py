@@ -9,7 +9,9 @@ feed-forward units per token, an optional shared unit runs for every token, and 
 
 The step's rows are sorted by expert on the device (``ops.MoePlan``); the experts' gate|up product
 gathers its rows from the tokens and applies the activation in its epilogue, the down product leaves
-float32 rows that one kernel sums per token with the shared unit's output.  Nothing is read by the host,
+rows that one kernel sums per token, in float32, with the shared unit's output.  Steps with many rows run
+both products on the grouped tcgen05 kernel (row tiles of 128 per expert), steps with few on mma.sync
+tiles of 64 rows that read the chosen experts' weights once.  Nothing is read by the host,
 so steps with this part are captured as CUDA graphs like the others.
 """
 from __future__ import annotations
@@ -66,10 +68,16 @@ class MixtureOfExperts:
     def load(self, t: Dict[str, torch.Tensor]) -> None:
         gate, up, down = self.names
         self.w_router = t[self.router_name].contiguous()
+        # gate and up of an expert as one matrix, their rows interleaved by eight where the width allows
+        # (the layout whose products apply the activation in their epilogue), else stacked
+        self.interleaved = self.inter % 8 == 0
         stacks = []
         for e in range(self.experts):
             p = f"{self.expert_prefix}{e}."
-            stacks.append(torch.cat([t[p + gate], t[p + up]], dim=0))
+            if self.interleaved:
+                stacks.append(ops.interleave_gate_up(t[p + gate], t[p + up]))
+            else:
+                stacks.append(torch.cat([t[p + gate], t[p + up]], dim=0))
         self.w_gate_up = torch.stack(stacks).contiguous()                       # [E, 2 I, H]
         self.w_down = torch.stack([t[f"{self.expert_prefix}{e}.{down}"] for e in range(self.experts)]).contiguous()
         if self.shared is not None:
@@ -84,10 +92,14 @@ class MixtureOfExperts:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         z = ops.linear(x, self.w_router, out_dtype=torch.float32)
         ids, weights = ops.moe_route(z, self.top, softmax_weights=self.router_scores == "softmax")
-        plan = ops.MoePlan(ids, self.experts)
+        rows = ids.numel()
+        tensor_cores = self.interleaved and x.dtype == self.w_gate_up.dtype \
+            and ops.moe_tcgen05_pays(rows, self.experts, self.inter, self.hidden, x.dtype)
+        plan = ops.MoePlan(ids, self.experts, ops.MOE_TCGEN05_TILE if tensor_cores else None)
         on_input = self.weight_on == "input"
         act = ops.moe_grouped(x, self.w_gate_up, plan, self.top, gated=True, gather=True,
-                              weights=weights if on_input else None, act=self.activation)
+                              weights=weights if on_input else None, act=self.activation,
+                              interleaved=self.interleaved)
         y = ops.moe_grouped(act, self.w_down, plan, self.top, gated=False, gather=False)
         shared = self.shared.forward(x, ctx) if self.shared is not None else None
         return ops.moe_combine(y, plan, self.top, shared, self.dtype, weights=None if on_input else weights)
