@@ -223,11 +223,12 @@ __device__ __forceinline__ float fast_tanh(float x) {
     return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
 }
 
-// The modified score times log2(e), for exp2f.
-__device__ __forceinline__ float mod_score_fast(float dot, float slope, int dist, const ScoreMod& m) {
+// The modified score times log2(e), for exp2f.  `dist` comes as a float and 1 / cap as a factor: a
+// conversion or a division per score would go through the same slow unit as the exponentials.
+__device__ __forceinline__ float mod_score_fast(float dot, float slope_log2e, float dist, const ScoreMod& m, float inv_cap) {
     float s = dot * m.scale;
-    if (m.softcap > 0.0f) s = m.softcap * fast_tanh(__fdividef(s, m.softcap));
-    return (s - slope * (float)dist) * kLog2e;
+    if (m.softcap > 0.0f) s = m.softcap * fast_tanh(s * inv_cap);
+    return s * kLog2e - slope_log2e * dist;
 }
 
 // ---------------------------------------------------------------- prompt portions, bfloat16, mma.sync
@@ -238,7 +239,7 @@ __device__ __forceinline__ float mod_score_fast(float dot, float slope, int dist
 constexpr int kPfWarps = 4, kPfM = 64, kPfN = 64, kPfPad = 8;
 
 template <int DKP, int DVP>
-__global__ void __launch_bounds__(kPfWarps * 32, 2)
+__global__ void __launch_bounds__(kPfWarps * 32, 3)
 attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
                                 const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                 const int* __restrict__ block_table, int max_pages, int page_size,
@@ -256,7 +257,8 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = head / (q_heads / kv_heads);
     const int* table = block_table + (size_t)slot * max_pages;
-    const float slope = slopes != nullptr ? slopes[head] : 0.0f;
+    const float slope2 = (slopes != nullptr ? slopes[head] : 0.0f) * kLog2e;
+    const float inv_cap = mod.softcap > 0.0f ? 1.0f / mod.softcap : 0.0f;
 
     const int rows_here = min(kPfM, len - q_off);
     const int first_pos = pos0 + q_off, last_pos = first_pos + rows_here - 1;
@@ -352,14 +354,16 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
                 }
             }
             const int key_base = key0 + (lane & 3) * 2;
+            const float d_lo = (float)(p_lo - key_base), d_hi = (float)(p_hi - key_base);
             float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
 #pragma unroll
             for (int nt = 0; nt < kPfN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = key_base + nt * 8 + e;
-                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score_fast(s[nt][e], slope, p_lo - j, mod) : -INFINITY;
-                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score_fast(s[nt][2 + e], slope, p_hi - j, mod) : -INFINITY;
+                    const float back = (float)(nt * 8 + e);          // a constant once the loops are unrolled
+                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score_fast(s[nt][e], slope2, d_lo - back, mod, inv_cap) : -INFINITY;
+                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score_fast(s[nt][2 + e], slope2, d_hi - back, mod, inv_cap) : -INFINITY;
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
                     tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
                 }
@@ -506,8 +510,9 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
 
     const int r_lo = lane >> 2, r_hi = r_lo + 8;                       // rows of the tile: heads of the group
     const bool v_lo = r_lo < group, v_hi = r_hi < group;
-    const float slope_lo = (slopes != nullptr && v_lo) ? slopes[head0 + r_lo] : 0.0f;
-    const float slope_hi = (slopes != nullptr && v_hi) ? slopes[head0 + r_hi] : 0.0f;
+    const float slope_lo = (slopes != nullptr && v_lo) ? slopes[head0 + r_lo] * kLog2e : 0.0f;
+    const float slope_hi = (slopes != nullptr && v_hi) ? slopes[head0 + r_hi] * kLog2e : 0.0f;
+    const float inv_cap = mod.softcap > 0.0f ? 1.0f / mod.softcap : 0.0f;
     const bf16* q_lo = q + ((size_t)t * q_heads + head0 + r_lo) * dk;
     const bf16* q_hi = q + ((size_t)t * q_heads + head0 + r_hi) * dk;
     uint32_t qa[DKP / 16][4];
@@ -583,6 +588,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                 }
             }
             const int key_base = key0 + (lane & 3) * 2;
+            const float d0 = (float)(pos - key_base);
             float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
@@ -590,8 +596,9 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                 for (int e = 0; e < 2; ++e) {
                     const int j = key_base + nt * 8 + e;
                     const bool seen = j <= pos && j >= lo;
-                    s[nt][e] = (seen && v_lo) ? mod_score_fast(s[nt][e], slope_lo, pos - j, mod) : -INFINITY;
-                    s[nt][2 + e] = (seen && v_hi) ? mod_score_fast(s[nt][2 + e], slope_hi, pos - j, mod) : -INFINITY;
+                    const float dist = d0 - (float)(nt * 8 + e);
+                    s[nt][e] = (seen && v_lo) ? mod_score_fast(s[nt][e], slope_lo, dist, mod, inv_cap) : -INFINITY;
+                    s[nt][2 + e] = (seen && v_hi) ? mod_score_fast(s[nt][2 + e], slope_hi, dist, mod, inv_cap) : -INFINITY;
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
                     tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
                 }
