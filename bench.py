@@ -621,6 +621,20 @@ def design_bench(args) -> int:
     ms = timed(experts)
     kern["moe_grouped_products_2048_tokens"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
                                                 "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+    # four times the rows: an expert's 128-row tiles are then mostly full (at 2048 tokens an expert gets 128 rows
+    # on average, so nearly every expert has a second, almost empty tile)
+    T4 = 4 * T
+    x4 = torch.randn(T4, W, device=device).to(bf)
+    ids4, wts4 = ops.moe_route(torch.randn(T4, E, device=device), top)
+    plan4 = ops.MoePlan(ids4, E, ops.MOE_TCGEN05_TILE if ops.moe_tcgen05_pays(T4 * top, E, I, W, bf) else None)
+
+    def experts4():
+        a = ops.moe_grouped(x4, w_gu, plan4, top, gated=True, gather=True, weights=wts4, interleaved=True)
+        return ops.moe_grouped(a, w_d, plan4, top, gated=False, gather=False)
+    ms = timed(experts4)
+    kern["moe_grouped_products_8192_tokens"] = {"us": round(ms * 1e3, 1), "tflops": round(4 * flops / ms / 1e9, 1),
+                                                "frac_tensor": round(4 * flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+    del x4, ids4, wts4, plan4
     wd_gu = ops.interleave_gate_up(*(torch.randn(2, top * I, W, device=device) * 0.02).to(bf)).contiguous()
     wd_d = (torch.randn(W, top * I, device=device) * 0.02).to(bf)
     ms = timed(lambda: ops.linear(ops.linear_swiglu(x, wd_gu, bf, interleaved=True), wd_d, out_dtype=bf))

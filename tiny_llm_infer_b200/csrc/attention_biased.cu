@@ -29,6 +29,12 @@ struct ScoreMod {
     int chunk, window, sink;
 };
 
+static inline int page_shift_of(int page_size) {
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    return (1 << shift) == page_size ? shift : -1;
+}
+
 __device__ __forceinline__ int first_key(int pos, const ScoreMod& m) {
     int lo = 0;
     if (m.chunk > 0) lo = (pos / m.chunk) * m.chunk;
@@ -223,11 +229,30 @@ __device__ __forceinline__ float fast_tanh(float x) {
     return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f);
 }
 
+// 2^x by the hardware approximation alone (exp2f adds a range reduction for denormal results; here a
+// weight that small is zero anyway).  2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Page and place in the page of a key: a shift and a mask where the page size is a power of two
+// (`shift` >= 0), else a division.
+__device__ __forceinline__ void page_of(int key, int page_size, int shift, int& page_index, int& in_page) {
+    if (shift >= 0) { page_index = key >> shift; in_page = key & (page_size - 1); }
+    else { page_index = key / page_size; in_page = key - page_index * page_size; }
+}
+
 // The modified score times log2(e), for exp2f.  `dist` comes as a float and 1 / cap as a factor: a
-// conversion or a division per score would go through the same slow unit as the exponentials.
+// conversion or a division per score would go through the same slow unit as the exponentials.  No
+// branch: the capped and the plain score are both made and one is kept, so that the scores of a tile
+// are independent chains the scheduler can interleave (with the mask as a condition around the
+// arithmetic every score was a branch of its own, and the chains ran one after the other).
 __device__ __forceinline__ float mod_score_fast(float dot, float slope_log2e, float dist, const ScoreMod& m, float inv_cap) {
-    float s = dot * m.scale;
-    if (m.softcap > 0.0f) s = m.softcap * fast_tanh(s * inv_cap);
+    const float plain = dot * m.scale;
+    const float capped = m.softcap * fast_tanh(plain * inv_cap);
+    const float s = m.softcap > 0.0f ? capped : plain;
     return s * kLog2e - slope_log2e * dist;
 }
 
@@ -243,7 +268,7 @@ __global__ void __launch_bounds__(kPfWarps * 32, 3)
 attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
                                 const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                 const int* __restrict__ block_table, int max_pages, int page_size,
-                                int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
+                                int page_shift, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
                                 const float* __restrict__ slopes, const bf16* gate, int gate_stride,
                                 bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
@@ -283,6 +308,7 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
     const int w_first = first_pos + warp * 16;
     const int w_last = min(w_first + 15, last_pos);
     const int w_lo = first_key(w_first, mod);
+    const int w_hi_lo = first_key(w_first + 15, mod);                  // the latest first key among the warp's rows
 
     float o[DVP / 8][4];
 #pragma unroll
@@ -298,10 +324,12 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
         // a thread keeps its 16-byte column and walks the rows: one look-up of the page per row
         for (int row = threadIdx.x / kKC, chunk = threadIdx.x % kKC; row < kPfN; row += kPfWarps * 32 / kKC) {
             const int key = kt * kPfN + row;
-            const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
+            int page_index, place;
+            page_of(key, page_size, page_shift, page_index, place);
+            const int page = (key <= last_pos && key >= lo_all) ? table[page_index] : -1;
             const bool ok = page >= 0;
             const long long page_at = ok ? (long long)page * page_stride : 0;
-            const long long in_page = (long long)g * page_size + key % page_size;
+            const long long in_page = (long long)g * page_size + place;
             const bool k_ok = ok && chunk * 8 < dk;
             cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
             if (kKC == kVC) {
@@ -312,15 +340,16 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
         if (kKC != kVC) {
             for (int row = threadIdx.x / kVC, chunk = threadIdx.x % kVC; row < kPfN; row += kPfWarps * 32 / kVC) {
                 const int key = kt * kPfN + row;
-                const int page = (key <= last_pos && key >= lo_all) ? table[key / page_size] : -1;
+                int page_index, place;
+                page_of(key, page_size, page_shift, page_index, place);
+                const int page = (key <= last_pos && key >= lo_all) ? table[page_index] : -1;
                 const bool v_ok = page >= 0 && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + key % page_size) * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * dv + chunk * 8 : 0), v_ok);
             }
         }
         cp_async_commit();
     };
 
-    const int k_steps = (dk + 15) / 16, v_pairs = (dv + 15) / 16;
     issue(kt_first, 0);
     for (int kt = kt_first; kt <= kt_last; ++kt) {
         const int stage = (kt - kt_first) & 1;
@@ -341,29 +370,43 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
 #pragma unroll
             for (int i = 0; i < kPfN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
-            for (int ks = 0; ks < DKP / 16; ++ks) {
-                if (ks < k_steps) {
+            for (int ks = 0; ks < DKP / 16; ++ks) {               // columns past dk are zeros on both sides
 #pragma unroll
-                    for (int nt2 = 0; nt2 < kPfN / 16; ++nt2) {
-                        uint32_t kb[4];
-                        ldmatrix_x4(kb, ks_base + ((nt2 * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
-                        const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
-                        mma_bf16_16816(s[2 * nt2], qa[ks], b0);
-                        mma_bf16_16816(s[2 * nt2 + 1], qa[ks], b1);
-                    }
+                for (int nt2 = 0; nt2 < kPfN / 16; ++nt2) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, ks_base + ((nt2 * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
+                    const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+                    mma_bf16_16816(s[2 * nt2], qa[ks], b0);
+                    mma_bf16_16816(s[2 * nt2 + 1], qa[ks], b1);
                 }
             }
             const int key_base = key0 + (lane & 3) * 2;
             const float d_lo = (float)(p_lo - key_base), d_hi = (float)(p_hi - key_base);
+            // a tile that every row of the warp sees whole needs no masks (most tiles of a long prompt)
+            const bool inner = key0 + kPfN - 1 <= w_first && key0 >= w_hi_lo;
             float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
 #pragma unroll
             for (int nt = 0; nt < kPfN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int j = key_base + nt * 8 + e;
                     const float back = (float)(nt * 8 + e);          // a constant once the loops are unrolled
-                    s[nt][e] = (j <= p_lo && j >= f_lo) ? mod_score_fast(s[nt][e], slope2, d_lo - back, mod, inv_cap) : -INFINITY;
-                    s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? mod_score_fast(s[nt][2 + e], slope2, d_hi - back, mod, inv_cap) : -INFINITY;
+                    s[nt][e] = mod_score_fast(s[nt][e], slope2, d_lo - back, mod, inv_cap);
+                    s[nt][2 + e] = mod_score_fast(s[nt][2 + e], slope2, d_hi - back, mod, inv_cap);
+                }
+            if (!inner) {
+#pragma unroll
+                for (int nt = 0; nt < kPfN / 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = key_base + nt * 8 + e;
+                        s[nt][e] = (j <= p_lo && j >= f_lo) ? s[nt][e] : -INFINITY;
+                        s[nt][2 + e] = (j <= p_hi && j >= f_hi) ? s[nt][2 + e] : -INFINITY;
+                    }
+            }
+#pragma unroll
+            for (int nt = 0; nt < kPfN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
                     tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
                 }
@@ -373,7 +416,7 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
             tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
             const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
             const float ms_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
-            const float c_lo = exp2f(m_lo - ms_lo), c_hi = exp2f(m_hi - ms_hi);
+            const float c_lo = fast_exp2(m_lo - ms_lo), c_hi = fast_exp2(m_hi - ms_hi);
             m_lo = mn_lo;
             m_hi = mn_hi;
             float sum_lo = 0.0f, sum_hi = 0.0f;
@@ -381,8 +424,8 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
             for (int nt = 0; nt < kPfN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    s[nt][e] = exp2f(s[nt][e] - ms_lo);
-                    s[nt][2 + e] = exp2f(s[nt][2 + e] - ms_hi);
+                    s[nt][e] = fast_exp2(s[nt][e] - ms_lo);
+                    s[nt][2 + e] = fast_exp2(s[nt][2 + e] - ms_hi);
                     sum_lo += s[nt][e];
                     sum_hi += s[nt][2 + e];
                 }
@@ -398,14 +441,12 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
                                         pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]),
                                         pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
 #pragma unroll
-                for (int c = 0; c < DVP / 8; c += 2) {
-                    if (c / 2 < v_pairs) {
-                        uint32_t vb[4];
-                        ldmatrix_x4_trans(vb, vs_base + ((kk * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
-                        const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
-                        mma_bf16_16816(o[c], pa, b0);
-                        mma_bf16_16816(o[c + 1], pa, b1);
-                    }
+                for (int c = 0; c < DVP / 8; c += 2) {             // value columns past dv are zeros
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vs_base + ((kk * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
+                    const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+                    mma_bf16_16816(o[c], pa, b0);
+                    mma_bf16_16816(o[c + 1], pa, b1);
                 }
             }
         }
@@ -460,7 +501,7 @@ static int launch_biased_prefill(const void* q, const void* kp, const void* vp, 
     }
     launch_pdl(kPdlAttention, attention_biased_prefill_kernel<DKP, DVP>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, seg_info, tiles,
-               block_table, max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
+               block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
                gate_stride, (bf16*)out);
     return finish_launch("attention_biased_prefill");
 }
@@ -478,7 +519,7 @@ __global__ void __launch_bounds__(kPfWarps * 32, 2)
 attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v_plane, long long page_stride,
                                const int* __restrict__ positions, const int* __restrict__ token_slot,
                                const int* __restrict__ rows, const int* __restrict__ block_table, int max_pages,
-                               int page_size, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
+                               int page_size, int page_shift, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
                                const float* __restrict__ slopes, const bf16* gate, int gate_stride,
                                int splits, float* part, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
@@ -537,10 +578,12 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
         constexpr int kKC = DKP / 8, kVC = DVP / 8;
         for (int row = threadIdx.x / kKC, chunk = threadIdx.x % kKC; row < kPfN; row += kPfWarps * 32 / kKC) {
             const int key = kt * kPfN + row;
-            const int page = (key <= pos && key >= lo) ? table[key / page_size] : -1;
+            int page_index, place;
+            page_of(key, page_size, page_shift, page_index, place);
+            const int page = (key <= pos && key >= lo) ? table[page_index] : -1;
             const bool ok = page >= 0;
             const long long page_at = ok ? (long long)page * page_stride : 0;
-            const long long in_page = (long long)g * page_size + key % page_size;
+            const long long in_page = (long long)g * page_size + place;
             const bool k_ok = ok && chunk * 8 < dk;
             cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
             if (kKC == kVC) {
@@ -551,15 +594,16 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
         if (kKC != kVC) {
             for (int row = threadIdx.x / kVC, chunk = threadIdx.x % kVC; row < kPfN; row += kPfWarps * 32 / kVC) {
                 const int key = kt * kPfN + row;
-                const int page = (key <= pos && key >= lo) ? table[key / page_size] : -1;
+                int page_index, place;
+                page_of(key, page_size, page_shift, page_index, place);
+                const int page = (key <= pos && key >= lo) ? table[page_index] : -1;
                 const bool v_ok = page >= 0 && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + key % page_size) * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * dv + chunk * 8 : 0), v_ok);
             }
         }
         cp_async_commit();
     };
 
-    const int k_steps = (dk + 15) / 16, v_pairs = (dv + 15) / 16;
     if (kt_first <= kt_last) issue(kt_first, 0);
     for (int kt = kt_first; kt <= kt_last; ++kt) {
         const int stage = (kt - kt_first) & 1;
@@ -579,13 +623,11 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
             s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
 #pragma unroll
             for (int ks = 0; ks < DKP / 16; ++ks) {
-                if (ks < k_steps) {
-                    uint32_t kb[4];
-                    ldmatrix_x4(kb, ks_base + ((warp * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
-                    const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
-                    mma_bf16_16816(s[0], qa[ks], b0);
-                    mma_bf16_16816(s[1], qa[ks], b1);
-                }
+                uint32_t kb[4];
+                ldmatrix_x4(kb, ks_base + ((warp * 16 + (mid >> 1) * 8 + mrow) * kKRow + ks * 16 + (mid & 1) * 8) * 2);
+                const uint32_t b0[2] = {kb[0], kb[1]}, b1[2] = {kb[2], kb[3]};
+                mma_bf16_16816(s[0], qa[ks], b0);
+                mma_bf16_16816(s[1], qa[ks], b1);
             }
             const int key_base = key0 + (lane & 3) * 2;
             const float d0 = (float)(pos - key_base);
@@ -597,8 +639,10 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                     const int j = key_base + nt * 8 + e;
                     const bool seen = j <= pos && j >= lo;
                     const float dist = d0 - (float)(nt * 8 + e);
-                    s[nt][e] = (seen && v_lo) ? mod_score_fast(s[nt][e], slope_lo, dist, mod, inv_cap) : -INFINITY;
-                    s[nt][2 + e] = (seen && v_hi) ? mod_score_fast(s[nt][2 + e], slope_hi, dist, mod, inv_cap) : -INFINITY;
+                    const float a = mod_score_fast(s[nt][e], slope_lo, dist, mod, inv_cap);
+                    const float b = mod_score_fast(s[nt][2 + e], slope_hi, dist, mod, inv_cap);
+                    s[nt][e] = (seen && v_lo) ? a : -INFINITY;
+                    s[nt][2 + e] = (seen && v_hi) ? b : -INFINITY;
                     tmax_lo = fmaxf(tmax_lo, s[nt][e]);
                     tmax_hi = fmaxf(tmax_hi, s[nt][2 + e]);
                 }
@@ -608,7 +652,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
             tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
             const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
             const float ms_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, ms_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
-            const float c_lo = exp2f(m_lo - ms_lo), c_hi = exp2f(m_hi - ms_hi);
+            const float c_lo = fast_exp2(m_lo - ms_lo), c_hi = fast_exp2(m_hi - ms_hi);
             m_lo = mn_lo;
             m_hi = mn_hi;
             float sum_lo = 0.0f, sum_hi = 0.0f;
@@ -616,8 +660,8 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    s[nt][e] = exp2f(s[nt][e] - ms_lo);
-                    s[nt][2 + e] = exp2f(s[nt][2 + e] - ms_hi);
+                    s[nt][e] = fast_exp2(s[nt][e] - ms_lo);
+                    s[nt][2 + e] = fast_exp2(s[nt][2 + e] - ms_hi);
                     sum_lo += s[nt][e];
                     sum_hi += s[nt][2 + e];
                 }
@@ -631,13 +675,11 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                                     pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
 #pragma unroll
             for (int c = 0; c < DVP / 8; c += 2) {
-                if (c / 2 < v_pairs) {
-                    uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, vs_base + ((warp * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
-                    const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
-                    mma_bf16_16816(o[c], pa, b0);
-                    mma_bf16_16816(o[c + 1], pa, b1);
-                }
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, vs_base + ((warp * 16 + (mid & 1) * 8 + mrow) * kVRow + (c + (mid >> 1)) * 8) * 2);
+                const uint32_t b0[2] = {vb[0], vb[1]}, b1[2] = {vb[2], vb[3]};
+                mma_bf16_16816(o[c], pa, b0);
+                mma_bf16_16816(o[c + 1], pa, b1);
             }
         }
         __syncthreads();
@@ -669,7 +711,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
 #pragma unroll
         for (int w = 0; w < kPfWarps; ++w) {
             const float* src = meet + ((size_t)w * group + h) * rec;
-            const float wt = src[dv] == -INFINITY ? 0.0f : exp2f(src[dv] - mm);
+            const float wt = src[dv] == -INFINITY ? 0.0f : fast_exp2(src[dv] - mm);
             total += src[dv + 1] * wt;
             v += src[e] * wt;
         }
@@ -706,7 +748,7 @@ __global__ void attention_biased_combine_kernel(const float* part, const int* __
         float total = 0.0f, v = 0.0f;
         for (int s2 = 0; s2 < splits; ++s2) {
             const float ms = src[s2 * rec + dv];
-            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+            const float w = ms == -INFINITY ? 0.0f : fast_exp2(ms - mm);
             total += src[s2 * rec + dv + 1] * w;
             v += src[s2 * rec + e] * w;
         }
@@ -732,7 +774,7 @@ static int launch_biased_decode(const void* q, const void* kp, const void* vp, l
     }
     launch_pdl(kPdlAttention, attention_biased_decode_kernel<DKP, DVP>, dim3(n_rows, kv_heads, splits), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, positions, token_slot,
-               rows, block_table, max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
+               rows, block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
                gate_stride, splits, part, (bf16*)out);
     if (splits > 1)
         launch_pdl(kPdlCombine, attention_biased_combine_kernel, dim3(n_rows, q_heads), dim3(dv >= 128 ? 128 : 64), 0, stream,
