@@ -99,3 +99,48 @@ def test_plain_router_weights_scale_the_input():
     t = 1
     want = sum(plain.gated_mlp((weights[t, k] * u[t])[None], w, f"m.e{int(idx[t, k])}.", plain.silu)[0] for k in range(2))
     assert torch.allclose(out[t], want, atol=1e-12)
+
+
+def test_pages_behind_a_chunk_go_back_and_never_a_page_a_later_query_reads():
+    """Two requests grow in uneven portions on a small pool: in the groups of chunked layers pages behind
+    the reach are given back while the request lives and used again, and at every moment every key that a
+    query at or after the computed length can still see (its own chunk from the chunk's first position) lies
+    on a page the request holds."""
+    import random
+    from tiny_llm_infer_b200.cache import CacheManager
+    cfg = PANOLORNS["P2"]["cfg"]                      # chunks of 24 and 7 beside a layer that keeps every key
+    model = Model(describe_model(cfg), torch.float32, "cpu")
+    page = 8
+    cache = CacheManager(model.cache_needs(), page, {24: 14, None: 40, 7: 10}, max_slots=2, max_seq_len=160,
+                         dtype=torch.float32, device=None)
+    rng = random.Random(3)
+    length = {"a": 0, "b": 0}
+    cache.admit("a")
+    cache.admit("b")
+    seen_pages = {24: set(), 7: set()}
+    reused = False
+    while min(length.values()) < 150:
+        name = rng.choice(["a", "b"])
+        n = min(160 - length[name], rng.choice([1, 1, 2, 3, 5, 13]))
+        if n <= 0:
+            continue
+        cache.reserve(name, length[name] + n)
+        cache.commit(name, length[name] + n)
+        length[name] += n
+        cache.audit()
+        for window, pages in cache.pages_of(name).items():
+            if window is None:
+                assert len(pages) == -(-length[name] // page)
+                continue
+            first_needed = (length[name] // window) * window if length[name] < 160 else length[name]
+            table = cache.groups[window].table[cache.slot_of(name)]
+            for key in range(first_needed, length[name]):
+                assert table[key // page] >= 0, (window, name, key)
+            assert len(pages) <= -(-window // page) + 2              # the reach, its ragged ends, the page ahead
+            reused = reused or any(p in seen_pages[window] for p in pages)
+            seen_pages[window].update(pages)
+    assert reused
+    cache.release("a")
+    cache.release("b")
+    cache.audit()
+    assert cache.free_pages() == {24: 14, None: 40, 7: 10}

@@ -35,7 +35,7 @@ F64 = torch.float64
 
 # ----------------------------------------------------------------------------- norms
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [100, 192, 4096 + 8])
+@pytest.mark.parametrize("width", [100, 200, 4096 + 8])
 def test_output_norm_fused_with_sum_and_next_norm(dtype, width):
     from tiny_llm_infer_b200 import ops
     torch.manual_seed(width)
@@ -96,7 +96,7 @@ def reference_attention(q, k, v, heads, kv_heads, scale, softcap, chunk, window,
 ATTENTION_CASES = [
     # heads, kv, dk, dv, page, chunk, window, softcap, sink, bias, gate
     dict(H=4, G=2, dk=64, dv=64, page=16, chunk=50, window=None, softcap=20.0, sink=True, bias=True, gate=True),
-    dict(H=8, G=1, dk=96, dv=96, page=32, chunk=120, window=None, softcap=50.0, sink=True, bias=True, gate=True),
+    dict(H=8, G=1, dk=80, dv=80, page=32, chunk=110, window=None, softcap=45.0, sink=True, bias=True, gate=True),
     dict(H=6, G=6, dk=32, dv=48, page=8, chunk=24, window=None, softcap=8.0, sink=True, bias=True, gate=True),
     dict(H=3, G=1, dk=40, dv=24, page=16, chunk=None, window=None, softcap=None, sink=True, bias=True, gate=False),
     dict(H=2, G=2, dk=128, dv=64, page=16, chunk=64, window=None, softcap=15.0, sink=True, bias=True, gate=True),
@@ -283,8 +283,9 @@ def test_products_with_the_activation_in_their_epilogue(act, rows):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,shared,inter,hidden", [(16, 1, 128, 64, 192), (5, 3, None, 40, 88),
-                                                             (8, 2, 96, 48, 128), (33, 4, 24, 72, 100)])
+@pytest.mark.parametrize("experts,top,shared,inter,hidden", [(16, 1, 112, 72, 176), (5, 3, None, 40, 88),
+                                                             (8, 2, 96, 48, 128), (33, 4, 24, 72, 100),
+                                                             (6, 2, 20, 36, 64)])
 def test_mixture_of_experts_alone(dtype, experts, top, shared, inter, hidden):
     from tiny_llm_infer_b200.parts.registry import lookup
     from tiny_llm_infer_b200.parts.spec import PartSpec
@@ -299,7 +300,7 @@ def test_mixture_of_experts_alone(dtype, experts, top, shared, inter, hidden):
     part = cls(dtype=dtype, device=DEV, **params)
     w = {}
     for name, spec in cls.param_specs(**params).items():
-        std = 1.0 if name == "router" else 0.25
+        std = 0.15 if name == "router" else 0.25          # logits of a few units: no sigmoid at 1 to the last bit
         w[name] = (torch.randn(spec.shape, generator=g) * std).to(dtype).to(DEV)
     part.load(dict(w))
     w64 = {"m." + k: v.double().cpu() for k, v in w.items()}
@@ -333,7 +334,7 @@ def test_router_takes_the_largest_and_the_lowest_index_on_ties():
 
 
 # ----------------------------------------------------------------------------- whole models, every way of cutting
-BF16_RMS = {"P1": 0.08, "P2": 0.11, "P3": 0.05}        # three times what a B200 shows (0.027, 0.038, 0.016)        # a row's root-mean-square difference over the row's spread
+BF16_RMS = {"P1": 0.08, "P2": 0.11, "P3": 0.06}        # three times what a B200 shows (0.027, 0.038, 0.019)        # a row's root-mean-square difference over the row's spread
 
 
 @pytest.fixture(scope="module", params=sorted(PANOLORNS))
@@ -502,3 +503,33 @@ def test_long_decoding_in_bfloat16_through_graphs(tmp_path):
                 for i, tok in enumerate(o.token_ids)]
         # a router's near-tie may fall the other way in bfloat16 and move a row by an expert's output
         assert sum(near) >= 0.9 * len(near), near
+
+
+def test_command_line_writes_and_runs_a_model(tmp_path):
+    """``bin/model_main``: a random Panolorn model from its config.json, greedy tokens equal to the plain
+    implementation's in float32, and seeded temperature / top-p sampling that repeats itself."""
+    import json
+    tiny = PANOLORNS["P2"]
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny["cfg"].to_dict()))
+    folder = tmp_path / "model"
+    tool = [sys.executable, str(ROOT / "bin" / "model_main")]
+    res = subprocess.run(tool + ["--write-random-model", str(folder), "--config", str(cfg_path), "--random-weights", "21",
+                                 "--weight-std", "0.07"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    cfg, w = plain.read_model(folder)
+    prompts = [prompt(40 + i, n, cfg["vocab"]) for i, n in enumerate((9, 31))]
+    ids = [a for p in prompts for a in ("--prompt-ids", ",".join(map(str, p)))]
+    common = tool + ["--infer", "--model", str(folder), "--max-seq-len", "128", "--max-new-tokens", "7"] + ids
+    res = subprocess.run(common + ["--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    got = [[int(x) for x in line.split(",")] for line in res.stdout.strip().splitlines()[-2:]]
+    assert got == [plain_greedy(cfg, w, p, 7) for p in prompts]
+    draws = []
+    for _ in range(2):
+        res = subprocess.run(common + ["--dtype", "bfloat16", "--temperature", "0.8", "--top-p", "0.9", "--seed", "5"],
+                             capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        draws.append(res.stdout.strip().splitlines()[-2:])
+    assert draws[0] == draws[1]
+    assert all(len(line.split(",")) == 7 and all(0 <= int(x) < cfg["vocab"] for x in line.split(",")) for line in draws[0])

@@ -39,11 +39,11 @@ P2 = dict(cfg=PanolornConfig(vocab=401, width=88, embedding_scale=1.0, norm_eps=
     layer(3, 1, 40, 24, 0.3, None, None, dense(100)),
     layer(6, 3, 32, 48, 0.4, 30.0, 7, moe(24, 12, 1, 56)),
 )), seed=12, std=0.08, norm_range=(0.6, 1.4), page_size=8, lengths=(70, 97, 41, 35, 66))
-# widths 96 (padded to 128 in the tensor-core kernel) and 128 / 64, eight query heads on one key/value head,
+# widths 80 (padded to 128 in the tensor-core kernel) and 128 / 64, eight query heads on one key/value head,
 # chunks longer than some requests and pages of 32
-P3 = dict(cfg=PanolornConfig(vocab=512, width=192, embedding_scale=13.0, norm_eps=1e-6, layers=(
-    layer(8, 1, 96, 96, 0.15, 50.0, 200, dense(256)),
-    layer(2, 2, 128, 64, 0.12, 15.0, 64, moe(64, 16, 2, 128)),
+P3 = dict(cfg=PanolornConfig(vocab=512, width=160, embedding_scale=11.0, norm_eps=1e-6, layers=(
+    layer(8, 1, 80, 80, 0.17, 40.0, 200, dense(320)),
+    layer(2, 2, 128, 64, 0.12, 15.0, 64, moe(56, 12, 2, 136)),
 )), seed=13, std=0.05, norm_range=(0.8, 1.2), page_size=32, lengths=(70, 300, 130, 41, 210, 35))
 PANOLORNS = {"P1": P1, "P2": P2, "P3": P3}
 
