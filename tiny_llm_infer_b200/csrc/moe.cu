@@ -12,6 +12,8 @@
 //            weight multiplies the expert's input) and apply act(gate) * up in its epilogue; bfloat16
 //            runs on mma.sync tiles (64 rows x 64 weight rows x 32 deep, operands prefetched through
 //            registers), float32 and odd sizes run one thread per output with the sum over k in order;
+//            steps with many rows take the grouped form of the tcgen05 product instead (gemm_tcgen05.cu),
+//            which reads its rows by TMA: `gather` lays the token rows out in the plan's order first;
 //   combine  out[t] = shared[t] + sum over the token's assignments of (weight *) y[row], in float32.
 //
 // A row's result does not depend on which other rows share its tile or its expert.
