@@ -37,6 +37,11 @@ class ModelConfig:
     def validate(self) -> None:  # pragma: no cover - interface
         raise NotImplementedError
 
+    def with_tensor_shapes(self, shapes: Dict[str, tuple]) -> "ModelConfig":
+        """The configuration completed by sizes that config.json does not carry and the checkpoint's tensor
+        shapes do (``shapes``: name -> shape).  Most architectures have none."""
+        return self
+
 
 @dataclass
 class _Entry:
@@ -113,7 +118,16 @@ def load_config(model_dir) -> ModelConfig:
         raise ConfigError(f"{cfg_path}: not valid JSON ({exc})") from None
     if not isinstance(raw, dict):
         raise ConfigError(f"{cfg_path}: top level must be an object")
-    return config_from_dict(raw)
+    cfg = config_from_dict(raw)
+    if type(cfg).with_tensor_shapes is not ModelConfig.with_tensor_shapes:
+        from ..weights.safetensors_io import SafetensorsError, tensor_shapes
+        try:
+            shapes = tensor_shapes(path)
+        except SafetensorsError:
+            shapes = {}                      # a folder without weights: the configuration's own defaults stand
+        cfg = cfg.with_tensor_shapes(shapes)
+        cfg.validate()
+    return cfg
 
 
 def describe_model(config: ModelConfig):

@@ -4,8 +4,11 @@
 //   a distance bias s <- s - slope[head] * (pos_query - pos_key),
 //   a chunk mask   keys only from the query's own chunk of `chunk` positions (counted from 0),
 //   a window       keys pos - window + 1 .. pos,
-//   a sink         one more term exp(0) in the softmax's denominator that carries no value,
-// and after the softmax an output gate: out *= sigmoid(gate).  Every constant is an argument; a
+//   a sink         one more term in the softmax's denominator that carries no value: exp(0), or exp(z_h) with a
+//                  learned number z_h per query head (`sink_logit`; it is not scaled, capped or biased),
+// and after the softmax an output gate: out *= sigmoid(gate).  Values may also be the first dv elements of
+// wider rows (`v_row` elements from one value to the next; the attention over compressed vectors that serve
+// as keys and, in part, as values passes the key plane twice).  Every constant is an argument; a
 // zero (or a null pointer) switches its step off, and with all of them off this is plain causal
 // attention.
 //
@@ -111,8 +114,8 @@ __global__ void attention_biased_general_kernel(
     const T* q, const T* k_plane, const T* v_plane, long long page_stride,
     const int* __restrict__ positions, const int* __restrict__ token_slot,
     const int* __restrict__ block_table, int max_pages, int page_size, int q_heads, int kv_heads,
-    int dk, int dv, ScoreMod mod, const float* __restrict__ slopes, const T* gate, int gate_stride,
-    T* __restrict__ out) {
+    int dk, int dv, ScoreMod mod, const float* __restrict__ slopes, const float* __restrict__ sink_logit, int v_row,
+    const T* gate, int gate_stride, T* __restrict__ out) {
     extern __shared__ float smem[];
     TLLM_PDL_ENTER();
     float* qs = smem;                             // [dk]
@@ -137,8 +140,8 @@ __global__ void attention_biased_general_kernel(
     __syncthreads();
 
     const int* table = block_table + (size_t)slot * max_pages;
-    // the sink is a key of score 0 without a value; warp 0 starts from it
-    float m = (mod.sink && warp == 0) ? 0.0f : -INFINITY;
+    // the sink is a key of score 0 (or of the head's learned score) without a value; warp 0 starts from it
+    float m = (mod.sink && warp == 0) ? (sink_logit != nullptr ? sink_logit[head] : 0.0f) : -INFINITY;
     float l = (mod.sink && warp == 0) ? 1.0f : 0.0f;
     float acc[CV];
 #pragma unroll
@@ -149,7 +152,7 @@ __global__ void attention_biased_general_kernel(
         if (page < 0) continue;
         const size_t in_page = (size_t)g * page_size + (j % page_size);
         const T* kp = k_plane + (long long)page * page_stride + in_page * dk;
-        const T* vp = v_plane + (long long)page * page_stride + in_page * dv;
+        const T* vp = v_plane + (long long)page * page_stride + in_page * v_row;
         float dot = 0.0f;
 #pragma unroll
         for (int c = 0; c < CK; ++c) {
@@ -201,8 +204,8 @@ template <typename T>
 static int launch_general(const void* q, const void* kp, const void* vp, long long page_stride,
                           const int* positions, const int* token_slot, const int* block_table,
                           int max_pages, int page_size, int tokens, int q_heads, int kv_heads, int dk,
-                          int dv, ScoreMod mod, const float* slopes, const void* gate, int gate_stride,
-                          void* out, cudaStream_t stream) {
+                          int dv, ScoreMod mod, const float* slopes, const float* sink_logit, int v_row,
+                          const void* gate, int gate_stride, void* out, cudaStream_t stream) {
     const dim3 grid(q_heads, tokens), block(kGenWarps * 32);
     const size_t smem = ((size_t)dk + (size_t)kGenWarps * dv + 2 * kGenWarps) * sizeof(float);
     const int ck = (dk + 31) / 32, cv = (dv + 31) / 32;
@@ -210,7 +213,7 @@ static int launch_general(const void* q, const void* kp, const void* vp, long lo
 #define LAUNCH(C)                                                                                           \
     launch_pdl(kPdlAttention, attention_biased_general_kernel<T, C, C>, grid, block, smem, stream,          \
                (const T*)q, (const T*)kp, (const T*)vp, page_stride, positions, token_slot, block_table,    \
-               max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, (const T*)gate, gate_stride, (T*)out)
+               max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, (const T*)gate, gate_stride, (T*)out)
     if (c <= 1) LAUNCH(1);
     else if (c <= 2) LAUNCH(2);
     else if (c <= 4) LAUNCH(4);
@@ -269,8 +272,8 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
                                 const int* __restrict__ seg_info, const int* __restrict__ tiles,
                                 const int* __restrict__ block_table, int max_pages, int page_size,
                                 int page_shift, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
-                                const float* __restrict__ slopes, const bf16* gate, int gate_stride,
-                                bf16* __restrict__ out) {
+                                const float* __restrict__ slopes, const float* __restrict__ sink_logit, int v_row,
+                                const bf16* gate, int gate_stride, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
     TLLM_PDL_ENTER();
     constexpr int kKRow = DKP + kPfPad, kVRow = DVP + kPfPad;           // elements per padded row
@@ -313,8 +316,9 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
     float o[DVP / 8][4];
 #pragma unroll
     for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    // the sink: a key of score 0 without a value, counted once per row (by the first lane of its four)
-    float m_lo = mod.sink ? 0.0f : -INFINITY, m_hi = m_lo;
+    // the sink: a key of score 0 (or the head's learned score) without a value, counted once per row (by the
+    // first lane of its four)
+    float m_lo = mod.sink ? (sink_logit != nullptr ? sink_logit[head] * kLog2e : 0.0f) : -INFINITY, m_hi = m_lo;
     float l_lo = (mod.sink && (lane & 3) == 0) ? 1.0f : 0.0f, l_hi = l_lo;
 
     auto issue = [&](int kt, int stage) {
@@ -334,7 +338,7 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
             cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
             if (kKC == kVC) {
                 const bool v_ok = ok && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * v_row + chunk * 8 : 0), v_ok);
             }
         }
         if (kKC != kVC) {
@@ -344,7 +348,7 @@ attention_biased_prefill_kernel(const bf16* q, const bf16* k_plane, const bf16* 
                 page_of(key, page_size, page_shift, page_index, place);
                 const int page = (key <= last_pos && key >= lo_all) ? table[page_index] : -1;
                 const bool v_ok = page >= 0 && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * v_row + chunk * 8 : 0), v_ok);
             }
         }
         cp_async_commit();
@@ -489,8 +493,8 @@ template <int DKP, int DVP>
 static int launch_biased_prefill(const void* q, const void* kp, const void* vp, long long page_stride,
                                  const int* seg_info, const int* tiles, int n_tiles, const int* block_table,
                                  int max_pages, int page_size, int q_heads, int kv_heads, int dk, int dv,
-                                 ScoreMod mod, const float* slopes, const void* gate, int gate_stride, void* out,
-                                 cudaStream_t stream) {
+                                 ScoreMod mod, const float* slopes, const float* sink_logit, int v_row, const void* gate,
+                                 int gate_stride, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)2 * kPfN * ((DKP + kPfPad) + (DVP + kPfPad)) * 2;
     static OncePerDevice configured;
     if (configured.first()) {
@@ -501,8 +505,8 @@ static int launch_biased_prefill(const void* q, const void* kp, const void* vp, 
     }
     launch_pdl(kPdlAttention, attention_biased_prefill_kernel<DKP, DVP>, dim3(n_tiles, q_heads), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, seg_info, tiles,
-               block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
-               gate_stride, (bf16*)out);
+               block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row,
+               (const bf16*)gate, gate_stride, (bf16*)out);
     return finish_launch("attention_biased_prefill");
 }
 
@@ -520,8 +524,8 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                                const int* __restrict__ positions, const int* __restrict__ token_slot,
                                const int* __restrict__ rows, const int* __restrict__ block_table, int max_pages,
                                int page_size, int page_shift, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
-                               const float* __restrict__ slopes, const bf16* gate, int gate_stride,
-                               int splits, float* part, bf16* __restrict__ out) {
+                               const float* __restrict__ slopes, const float* __restrict__ sink_logit, int v_row,
+                               const bf16* gate, int gate_stride, int splits, float* part, bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
     TLLM_PDL_ENTER();
     constexpr int kKRow = DKP + kPfPad, kVRow = DVP + kPfPad;
@@ -570,6 +574,10 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
     for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     const bool first = mod.sink && warp == 0 && split == 0;
     float m_lo = first ? 0.0f : -INFINITY, m_hi = m_lo;
+    if (first && sink_logit != nullptr) {            // the heads' learned sink scores, in base 2 like the scores
+        m_lo = v_lo ? sink_logit[head0 + r_lo] * kLog2e : 0.0f;
+        m_hi = v_hi ? sink_logit[head0 + r_hi] * kLog2e : 0.0f;
+    }
     float l_lo = (first && (lane & 3) == 0) ? 1.0f : 0.0f, l_hi = l_lo;
 
     auto issue = [&](int kt, int stage) {
@@ -588,7 +596,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
             cp_async_16(ks + (row * kKRow + chunk * 8) * 2, k_plane + (k_ok ? page_at + in_page * dk + chunk * 8 : 0), k_ok);
             if (kKC == kVC) {
                 const bool v_ok = ok && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? page_at + in_page * v_row + chunk * 8 : 0), v_ok);
             }
         }
         if (kKC != kVC) {
@@ -598,7 +606,7 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                 page_of(key, page_size, page_shift, page_index, place);
                 const int page = (key <= pos && key >= lo) ? table[page_index] : -1;
                 const bool v_ok = page >= 0 && chunk * 8 < dv;
-                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * dv + chunk * 8 : 0), v_ok);
+                cp_async_16(vs + (row * kVRow + chunk * 8) * 2, v_plane + (v_ok ? (long long)page * page_stride + ((long long)g * page_size + place) * v_row + chunk * 8 : 0), v_ok);
             }
         }
         cp_async_commit();
@@ -762,8 +770,8 @@ template <int DKP, int DVP>
 static int launch_biased_decode(const void* q, const void* kp, const void* vp, long long page_stride,
                                 const int* positions, const int* token_slot, const int* rows, int n_rows,
                                 const int* block_table, int max_pages, int page_size, int q_heads, int kv_heads,
-                                int dk, int dv, ScoreMod mod, const float* slopes, const void* gate,
-                                int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
+                                int dk, int dv, ScoreMod mod, const float* slopes, const float* sink_logit, int v_row,
+                                const void* gate, int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
     const size_t smem = (size_t)2 * kPfN * ((DKP + kPfPad) + (DVP + kPfPad)) * 2;      // also holds the warps' meeting
     static OncePerDevice configured;
     if (configured.first()) {
@@ -774,8 +782,8 @@ static int launch_biased_decode(const void* q, const void* kp, const void* vp, l
     }
     launch_pdl(kPdlAttention, attention_biased_decode_kernel<DKP, DVP>, dim3(n_rows, kv_heads, splits), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, positions, token_slot,
-               rows, block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, (const bf16*)gate,
-               gate_stride, splits, part, (bf16*)out);
+               rows, block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row,
+               (const bf16*)gate, gate_stride, splits, part, (bf16*)out);
     if (splits > 1)
         launch_pdl(kPdlCombine, attention_biased_combine_kernel, dim3(n_rows, q_heads), dim3(dv >= 128 ? 128 : 64), 0, stream,
                    (const float*)part, token_slot, rows, q_heads, dv, splits, (const bf16*)gate, gate_stride, (bf16*)out);
@@ -818,7 +826,9 @@ int tllm_attention_biased_general(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* block_table, int max_pages, int page_size, int dtype, int tokens,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(v_row >= dv, "attention_biased: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0,
                  "attention_biased: %d query heads over %d key/value heads", q_heads, kv_heads);
     TLLM_REQUIRE(dk > 0 && dk <= 512 && dv > 0 && dv <= 512, "attention_biased: widths %d, %d outside 1..512", dk, dv);
@@ -829,10 +839,10 @@ int tllm_attention_biased_general(
     const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
     if (dtype == kBF16)
         return launch_general<bf16>(q, k_plane, v_plane, page_stride, positions, token_slot, block_table, max_pages,
-                                    page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream);
+                                    page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream);
     if (dtype == kF32)
         return launch_general<float>(q, k_plane, v_plane, page_stride, positions, token_slot, block_table, max_pages,
-                                     page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream);
+                                     page_size, tokens, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream);
     TLLM_REQUIRE(false, "attention_biased: unknown dtype %d", dtype);
 }
 
@@ -848,7 +858,9 @@ int tllm_attention_biased_prefill(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* seg_info,
     const int* tiles, int n_tiles, const int* block_table, int max_pages, int page_size, int q_heads,
     int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, void* out, cudaStream_t stream) {
+    if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_prefill: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_prefill: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_tiles >= 0 && q_heads <= 65535, "attention_biased_prefill: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_prefill: negative constant");
@@ -856,7 +868,7 @@ int tllm_attention_biased_prefill(
     if (n_tiles == 0) return 0;
     const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
 #define PF(A, B) launch_biased_prefill<A, B>(q, k_plane, v_plane, page_stride, seg_info, tiles, n_tiles, block_table, max_pages, \
-                                             page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride, out, stream)
+                                             page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, out, stream)
     if (dk <= 64) return dv <= 64 ? PF(64, 64) : PF(64, 128);
     return dv <= 64 ? PF(128, 64) : PF(128, 128);
 #undef PF
@@ -868,7 +880,10 @@ int tllm_attention_biased_decode(
     const void* q, const void* k_plane, const void* v_plane, long long page_stride, const int* positions,
     const int* token_slot, const int* rows, int n_rows, const int* block_table, int max_pages, int page_size,
     int q_heads, int kv_heads, int dk, int dv, float scale, float softcap, int chunk, int window, int sink,
-    const float* slopes, const void* gate, int gate_stride, int splits, float* part, void* out, cudaStream_t stream) {
+    const float* slopes, const float* sink_logit, int v_row, const void* gate, int gate_stride, int splits, float* part,
+    void* out, cudaStream_t stream) {
+    if (v_row <= 0) v_row = dv;
+    TLLM_REQUIRE(v_row >= dv && v_row % 8 == 0, "attention_biased_decode: values of width %d in rows of %d", dv, v_row);
     TLLM_REQUIRE(tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv), "attention_biased_decode: sizes %d/%d heads, widths %d/%d", q_heads, kv_heads, dk, dv);
     TLLM_REQUIRE(page_size > 0 && max_pages > 0 && n_rows >= 0 && kv_heads <= 65535, "attention_biased_decode: bad geometry");
     TLLM_REQUIRE(chunk >= 0 && window >= 0 && softcap >= 0.0f, "attention_biased_decode: negative constant");
@@ -876,7 +891,7 @@ int tllm_attention_biased_decode(
     if (n_rows == 0) return 0;
     const ScoreMod mod{scale, softcap, chunk, window, sink ? 1 : 0};
 #define DEC(A, B) launch_biased_decode<A, B>(q, k_plane, v_plane, page_stride, positions, token_slot, rows, n_rows, block_table, \
-                                             max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, gate, gate_stride,    \
+                                             max_pages, page_size, q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row, gate, gate_stride, \
                                              splits, part, out, stream)
     if (dk <= 64) return dv <= 64 ? DEC(64, 64) : DEC(64, 128);
     return dv <= 64 ? DEC(128, 64) : DEC(128, 128);

@@ -344,6 +344,107 @@ __global__ void swiglu_vec_kernel(const T* gu, T* out, int inter, int interleave
     }
 }
 
+// ---------------------------------------------------------------- embedding + learned position + norm
+// v = table[ids[t], :] * scale + pos_table[positions[t], :] (the position part only if a table is given);
+// out[t, :] = gain * v / sqrt(mean(v^2) + eps) if a gain is given, else v.  All in float32; `gain` is
+// float32 and holds the factor itself.  Rows with ids[t] < 0 become zero.
+template <typename TW>
+__global__ void embedding_norm_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                      const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                                      const float* __restrict__ gain, float eps, float scale, float* __restrict__ out,
+                                      int hidden, int vocab, int max_positions) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    float* dst = out + (size_t)t * hidden;
+    if (id < 0) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    if (id >= vocab) id = vocab - 1;
+    const TW* src = table + (size_t)id * hidden;
+    const TW* prow = nullptr;
+    if (pos_table != nullptr) {
+        int p = positions[t];
+        p = p < 0 ? 0 : (p >= max_positions ? max_positions - 1 : p);     // the host refuses positions past the table
+        prow = pos_table + (size_t)p * hidden;
+    }
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = to_f32<TW>(src[i]) * scale;
+        if (prow != nullptr) v += to_f32<TW>(prow[i]);
+        dst[i] = v;
+        sum += v * v;
+    }
+    if (gain == nullptr) return;
+    sum = block_sum(sum, scratch);
+    const float sc = 1.0f / sqrtf(sum / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = dst[i] * sc * gain[i];
+}
+
+// ---------------------------------------------------------------- residual sum without a norm behind it
+// For blocks whose sub-layers read the stream itself: h[r, :] += d' and out[r, :] = h[r, :] in the storage
+// type, with d' = delta, or, with `post_gain`, post_gain * delta / sqrt(mean(delta^2) + post_eps) in float32.
+template <typename TD, typename TG, typename TO>
+__global__ void stream_add_kernel(float* h, const TD* delta, const TG* __restrict__ post_gain, float post_eps,
+                                  TO* __restrict__ out, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * width;
+    TO* dst = out + (size_t)r * width;
+    if (delta == nullptr) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_f32<TO>(hr[i]);
+        return;
+    }
+    const TD* dr = delta + (size_t)r * width;
+    float post_scale = 1.0f;
+    if (post_gain != nullptr) {
+        float sum = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = to_f32<TD>(dr[i]); sum += d * d; }
+        sum = block_sum(sum, scratch);
+        post_scale = 1.0f / sqrtf(sum / (float)width + post_eps);
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float d = to_f32<TD>(dr[i]);
+        if (post_gain != nullptr) d = d * post_scale * to_f32<TG>(post_gain[i]);
+        const float v = hr[i] + d;
+        hr[i] = v;
+        dst[i] = from_f32<TO>(v);
+    }
+}
+
+// ---------------------------------------------------------------- activations
+// out = act(x) (codes of `gate_act`), or, with a table, out[t, j] = act(x[t, j]) * table[ids[t], col0 + j]:
+// a gate on a per-token vector looked up by the token's id.
+template <typename T>
+__global__ void activation_kernel(const T* x, T* out, int act, int width, size_t total, const int* __restrict__ ids,
+                                  const T* __restrict__ table, int ldt, int col0, int vocab) {
+    TLLM_PDL_ENTER();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        float v = gate_act(to_f32<T>(x[idx]), act);
+        if (table != nullptr) {
+            const size_t t = idx / width, j = idx - t * width;
+            int id = ids[t];
+            if (id < 0) { out[idx] = from_f32<T>(0.0f); continue; }
+            if (id >= vocab) id = vocab - 1;
+            v *= to_f32<T>(table[(size_t)id * ldt + col0 + j]);
+        }
+        out[idx] = from_f32<T>(v);
+    }
+}
+
+// x <- cap * tanh(x / cap), in place (a bound on logits).
+__global__ void softcap_kernel(float* x, float cap, float inv_cap, size_t n) {
+    TLLM_PDL_ENTER();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < n; idx += stride) x[idx] = cap * tanhf(x[idx] * inv_cap);
+}
+
 __global__ void feed_tokens_kernel(int* ids, const int* places, const int* rows, const int* sampled, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) ids[places[i]] = sampled[rows[i]];
@@ -446,6 +547,68 @@ int tllm_embedding(const int* ids, const void* table, int table_dtype, float* ou
         else launch_pdl(kPdlOther, embedding_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, (const float*)table, out, hidden, vocab, scale);
     }
     return finish_launch("embedding");
+}
+
+// Embedding with an optional learned position table and an optional norm (gain in float32, the factor itself).
+int tllm_embedding_norm(const int* ids, const int* positions, const void* table, const void* pos_table, int table_dtype,
+                        const float* gain, float eps, float scale, float* out, int tokens, int hidden, int vocab,
+                        int max_positions, cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding_norm: bad sizes");
+    TLLM_REQUIRE(pos_table == nullptr || (positions != nullptr && max_positions > 0), "embedding_norm: a position table without positions");
+    TLLM_REQUIRE(gain == nullptr || eps > 0.0f, "embedding_norm: eps must be positive");
+    if (tokens == 0) return 0;
+    const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (table_dtype == kBF16)
+        launch_pdl(kPdlOther, embedding_norm_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, positions, (const bf16*)table,
+                   (const bf16*)pos_table, gain, eps, scale, out, hidden, vocab, max_positions);
+    else if (table_dtype == kF32)
+        launch_pdl(kPdlOther, embedding_norm_kernel<float>, dim3(tokens), dim3(block), 0, stream, ids, positions, (const float*)table,
+                   (const float*)pos_table, gain, eps, scale, out, hidden, vocab, max_positions);
+    else TLLM_REQUIRE(false, "embedding_norm: unknown dtype %d", table_dtype);
+    return finish_launch("embedding_norm");
+}
+
+// h += delta (normed first if `post_gain` is given) and out = h in the storage type `act_dtype` (also delta's).
+int tllm_stream_add(float* h, const void* delta, const void* post_gain, int gain_dtype, float post_eps, void* out,
+                    int act_dtype, int rows, int width, cudaStream_t stream) {
+    TLLM_REQUIRE(rows >= 0 && width > 0, "stream_add: bad sizes");
+    TLLM_REQUIRE(post_gain == nullptr || (delta != nullptr && post_eps > 0.0f), "stream_add: a gain without a delta or eps");
+    TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "stream_add: unknown gain dtype");
+    if (rows == 0) return 0;
+    const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+#define SADD(TD, TG, TO) launch_pdl(kPdlNorm, stream_add_kernel<TD, TG, TO>, dim3(rows), dim3(block), 0, stream, h, (const TD*)delta, \
+                                    (const TG*)post_gain, post_eps, (TO*)out, width)
+    if (act_dtype == kBF16) { if (gain_dtype == kBF16) SADD(bf16, bf16, bf16); else SADD(bf16, float, bf16); }
+    else if (act_dtype == kF32) { if (gain_dtype == kBF16) SADD(float, bf16, float); else SADD(float, float, float); }
+    else TLLM_REQUIRE(false, "stream_add: unknown dtype %d", act_dtype);
+#undef SADD
+    return finish_launch("stream_add");
+}
+
+int tllm_softcap(float* x, float cap, long long n, cudaStream_t stream) {
+    TLLM_REQUIRE(n >= 0 && cap > 0.0f, "softcap: bad arguments");
+    if (n == 0) return 0;
+    launch_pdl(kPdlOther, softcap_kernel, dim3(grid_for((size_t)n, 256)), dim3(256), 0, stream, x, cap, 1.0f / cap, (size_t)n);
+    return finish_launch("softcap");
+}
+
+// out = act(x), times table[ids[t], col0 + j] where a table is given (x and out [tokens, width]).
+int tllm_activation(const void* x, void* out, int dtype, int act, int tokens, int width, const int* ids,
+                    const void* table, int ldt, int col0, int vocab, cudaStream_t stream) {
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf, "activation: unknown activation %d", act);
+    TLLM_REQUIRE(tokens >= 0 && width > 0, "activation: bad sizes");
+    TLLM_REQUIRE(table == nullptr || (ids != nullptr && col0 >= 0 && col0 + width <= ldt && vocab > 0), "activation: bad table");
+    const size_t total = (size_t)tokens * width;
+    if (total == 0) return 0;
+    const int block = 256, grid = grid_for(total, block);
+    if (dtype == kBF16)
+        launch_pdl(kPdlSwiglu, activation_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)x, (bf16*)out, act, width, total,
+                   ids, (const bf16*)table, ldt, col0, vocab);
+    else if (dtype == kF32)
+        launch_pdl(kPdlSwiglu, activation_kernel<float>, dim3(grid), dim3(block), 0, stream, (const float*)x, (float*)out, act, width, total,
+                   ids, (const float*)table, ldt, col0, vocab);
+    else TLLM_REQUIRE(false, "activation: unknown dtype %d", dtype);
+    return finish_launch("activation");
 }
 
 // act_dtype is the storage type of both `delta` and `out`.

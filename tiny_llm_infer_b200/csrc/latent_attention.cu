@@ -1,0 +1,178 @@
+// Attention whose keys and values are made from one small vector per token (a latent c of width
+// `rank`) and one rotated key part of width `rot` that all heads share.  The cache holds [c | rotated
+// part] per token, one plane of one "head", and nothing per head.  The per-head matrices that would make
+// keys (Wk_h c) and values (Wv_h c) are moved to the query's side instead:
+//
+//   q_h . (Wk_h c) = (Wk_h^T q_h) . c            so the score is [Wk_h^T q_h | rotated q_h] . [c | rotated k]
+//   sum_j p_j (Wv_h c_j) = Wv_h (sum_j p_j c_j)  so the attention returns a mix of latents per head
+//
+// which makes the attention itself multi-query attention over the cached vectors (the paged kernels with
+// the modified score serve it: keys of width rank + rot, values the first `rank` elements of the same
+// rows).  This file has what goes around it:
+//
+//   latent_norm_store  per token: RMS norm of the query's latent (for the product that makes the queries),
+//                      RMS norm of c, rotation of the shared key part, write of [c | rotated] into its page.
+//   latent_query       per token and head: [Wk_h^T q_h (made by a batched product) | rotated part of q_h].
+//   heads_gate         per token: out[t, h, :] = x[h, t, :] * sigmoid(gate[t, h, :]), the batched product's
+//                      [heads, tokens, width] order turned back into rows.
+//
+// The rotation pairs neighbours (2i, 2i + 1) of the first `rot_dims` elements: (u, v) -> (u cos a - v sin a,
+// v cos a + u sin a) * mag, a = position * freq_i as a float32 product, cos and sin from the precise functions.
+#include "common.cuh"
+
+namespace tllm {
+
+template <typename T>
+__global__ void latent_norm_store_kernel(const T* proj, int ld, int q_rank, int rank, int rot, int rot_dims,
+                                         const float* __restrict__ q_gain, const float* __restrict__ c_gain,
+                                         float eps, const float* __restrict__ freq, float mag,
+                                         const int* __restrict__ positions, const int* __restrict__ token_slot,
+                                         const int* __restrict__ block_table, int max_pages, int page_size,
+                                         T* plane, long long page_stride, T* cq, int store) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0) {                           // a row without a request: a defined, harmless latent
+        for (int e = threadIdx.x; e < q_rank; e += blockDim.x) cq[(size_t)t * q_rank + e] = from_f32<T>(0.0f);
+        return;
+    }
+    const T* row = proj + (size_t)t * ld;
+    if (q_rank > 0) {
+        float sum = 0.0f;
+        for (int e = threadIdx.x; e < q_rank; e += blockDim.x) { const float x = to_f32<T>(row[e]); sum += x * x; }
+        sum = block_sum(sum, scratch);
+        const float sc = 1.0f / sqrtf(sum / (float)q_rank + eps);
+        for (int e = threadIdx.x; e < q_rank; e += blockDim.x)
+            cq[(size_t)t * q_rank + e] = from_f32<T>(to_f32<T>(row[e]) * sc * q_gain[e]);
+    }
+    if (!store) return;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+    if (page < 0) return;                     // no page held: nothing to write (the host reserves before a step)
+    T* dst = plane + (long long)page * page_stride + (size_t)(pos % page_size) * (rank + rot);
+    const T* c = row + q_rank;
+    float sum = 0.0f;
+    for (int e = threadIdx.x; e < rank; e += blockDim.x) { const float x = to_f32<T>(c[e]); sum += x * x; }
+    sum = block_sum(sum, scratch);
+    const float sc = 1.0f / sqrtf(sum / (float)rank + eps);
+    for (int e = threadIdx.x; e < rank; e += blockDim.x) dst[e] = from_f32<T>(to_f32<T>(c[e]) * sc * c_gain[e]);
+    const T* kr = c + rank;
+    for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+        const float a = (float)pos * freq[i];
+        const float cs = cosf(a) * mag, sn = sinf(a) * mag;
+        const float u = to_f32<T>(kr[2 * i]), v = to_f32<T>(kr[2 * i + 1]);
+        dst[rank + 2 * i] = from_f32<T>(u * cs - v * sn);
+        dst[rank + 2 * i + 1] = from_f32<T>(v * cs + u * sn);
+    }
+    for (int e = rot_dims + threadIdx.x; e < rot; e += blockDim.x) dst[rank + e] = kr[e];
+}
+
+// q [T, heads, plain + rot]; lat [heads, T, rank]; out [T, heads, rank + rot]
+template <typename T>
+__global__ void latent_query_kernel(const T* q, const T* lat, int heads, int plain, int rot, int rot_dims, int rank,
+                                    const float* __restrict__ freq, float mag, const int* __restrict__ positions,
+                                    const int* __restrict__ token_slot, int tokens, T* out) {
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const int width = rank + rot;
+    if (token_slot[t] < 0) {
+        for (int i = threadIdx.x; i < heads * width; i += blockDim.x) out[(size_t)t * heads * width + i] = from_f32<T>(0.0f);
+        return;
+    }
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+        const int h = i / width, e = i - h * width;
+        T* dst = out + ((size_t)t * heads + h) * width;
+        if (e < rank) {
+            dst[e] = lat[((size_t)h * tokens + t) * rank + e];
+            continue;
+        }
+        const int d = e - rank;
+        const T* src = q + ((size_t)t * heads + h) * (plain + rot) + plain;
+        if (d >= rot_dims) { dst[e] = src[d]; continue; }
+        const int pair = d >> 1;
+        const float a = (float)pos * freq[pair];
+        const float cs = cosf(a) * mag, sn = sinf(a) * mag;
+        const float u = to_f32<T>(src[2 * pair]), v = to_f32<T>(src[2 * pair + 1]);
+        dst[e] = from_f32<T>((d & 1) ? v * cs + u * sn : u * cs - v * sn);
+    }
+}
+
+// x [heads, T, width]; gate rows of stride ldg; out [T, heads * width]
+template <typename T>
+__global__ void heads_gate_kernel(const T* x, const T* gate, int ldg, int heads, int width, int tokens,
+                                  const int* __restrict__ token_slot, T* out) {
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const bool pad = token_slot != nullptr && token_slot[t] < 0;
+    for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+        const int h = i / width, e = i - h * width;
+        float v = 0.0f;
+        if (!pad) {
+            v = to_f32<T>(x[((size_t)h * tokens + t) * width + e]);
+            if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * ldg + i])));
+        }
+        out[(size_t)t * heads * width + i] = from_f32<T>(v);
+    }
+}
+
+}  // namespace tllm
+
+using namespace tllm;
+
+extern "C" {
+
+int tllm_latent_norm_store(const void* proj, int ld, int dtype, int q_rank, int rank, int rot, int rot_dims,
+                           const float* q_gain, const float* c_gain, float eps, const float* freq, float mag,
+                           const int* positions, const int* token_slot, const int* block_table, int max_pages,
+                           int page_size, void* plane, long long page_stride, void* cq, int store, int tokens,
+                           cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && q_rank >= 0 && rank > 0 && rot >= 0 && rot_dims >= 0 && rot_dims <= rot && rot_dims % 2 == 0,
+                 "latent_norm_store: bad sizes");
+    TLLM_REQUIRE(ld >= q_rank + rank + rot && eps > 0.0f, "latent_norm_store: rows too short");
+    TLLM_REQUIRE(!store || (plane && block_table && page_size > 0 && max_pages > 0), "latent_norm_store: no cache to write to");
+    TLLM_REQUIRE(q_rank == 0 || (cq != nullptr && q_gain != nullptr), "latent_norm_store: no place for the query's latent");
+    if (tokens == 0) return 0;
+#define STORE(T)                                                                                                   \
+    launch_pdl(kPdlQk, latent_norm_store_kernel<T>, dim3(tokens), dim3(128), 0, stream, (const T*)proj, ld, q_rank, \
+               rank, rot, rot_dims, q_gain, c_gain, eps, freq, mag, positions, token_slot, block_table, max_pages,  \
+               page_size, (T*)plane, page_stride, (T*)cq, store)
+    if (dtype == kBF16) STORE(bf16);
+    else if (dtype == kF32) STORE(float);
+    else TLLM_REQUIRE(false, "latent_norm_store: unknown dtype %d", dtype);
+#undef STORE
+    return finish_launch("latent_norm_store");
+}
+
+int tllm_latent_query(const void* q, const void* lat, int dtype, int heads, int plain, int rot, int rot_dims, int rank,
+                      const float* freq, float mag, const int* positions, const int* token_slot, int tokens, void* out,
+                      cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && heads > 0 && plain >= 0 && rot >= 0 && rank > 0 && rot_dims <= rot && rot_dims % 2 == 0,
+                 "latent_query: bad sizes");
+    if (tokens == 0) return 0;
+    if (dtype == kBF16)
+        launch_pdl(kPdlQk, latent_query_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)q, (const bf16*)lat, heads,
+                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (bf16*)out);
+    else if (dtype == kF32)
+        launch_pdl(kPdlQk, latent_query_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)q, (const float*)lat, heads,
+                   plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (float*)out);
+    else TLLM_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
+    return finish_launch("latent_query");
+}
+
+int tllm_heads_gate(const void* x, const void* gate, int ldg, int dtype, int heads, int width, int tokens,
+                    const int* token_slot, void* out, cudaStream_t stream) {
+    TLLM_REQUIRE(tokens >= 0 && heads > 0 && width > 0 && (gate == nullptr || ldg >= heads * width), "heads_gate: bad sizes");
+    if (tokens == 0) return 0;
+    if (dtype == kBF16)
+        launch_pdl(kPdlOther, heads_gate_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, ldg,
+                   heads, width, tokens, token_slot, (bf16*)out);
+    else if (dtype == kF32)
+        launch_pdl(kPdlOther, heads_gate_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)x, (const float*)gate, ldg,
+                   heads, width, tokens, token_slot, (float*)out);
+    else TLLM_REQUIRE(false, "heads_gate: unknown dtype %d", dtype);
+    return finish_launch("heads_gate");
+}
+
+}  // extern "C"

@@ -463,7 +463,15 @@ class ModelRunner:
             token_slot=d[2 * bucket:3 * bucket], want_rows=d[3 * bucket:4 * bucket], segments=[],
             seg_info=None, dec_rows=None, n_dec=bucket, pf_tiles=d[0:0].view(-1, 2), n_tiles=0,
             decode_only=True, max_context=ctx_bucket, max_segment=1)
-        self.model.forward(ctx, self.cache)          # warm-up: sizes workspaces, loads kernels
+        # warm-up: sizes workspaces, loads kernels.  A mixer with a per-request state would apply this step to
+        # it twice (here and in the replay), so then the warm-up runs with every row marked as padding
+        slots = d[2 * bucket:3 * bucket]
+        saved = slots.clone() if self.cache.state else None
+        if saved is not None:
+            slots.fill_(-1)
+        self.model.forward(ctx, self.cache)
+        if saved is not None:
+            slots.copy_(saved)
         torch.cuda.current_stream().synchronize()
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()

@@ -116,7 +116,10 @@ class Model:
         gives the ``LayerCacheView`` of a visit's mixer (a list of them for a block with several)."""
         if hasattr(ctx, "memo"):
             ctx.memo.clear()
-        h = self.embedding.forward(ctx.token_ids)
+        if getattr(self.embedding, "takes_context", False):
+            h = self.embedding.forward(ctx.token_ids, ctx)     # positions, and what it shares with the layers
+        else:
+            h = self.embedding.forward(ctx.token_ids)
         pending = None
         for layer, cache_ids, writes in self.order:
             views = [caches.view(cache_id, writes) for cache_id in cache_ids]

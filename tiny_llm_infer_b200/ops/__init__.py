@@ -66,11 +66,23 @@ def _declare(h) -> None:
         "tllm_qkv_unit_store": [vp, i32, vp, vp, f32, i32, vp, vp, vp, i32, i32, vp, vp, i64, vp, i32, i32,
                                 i32, i32, i32, i32, i32, vp],
         "tllm_attention_biased_general": [vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
         "tllm_attention_biased_prefill": [vp, vp, vp, i64, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, vp],
+                                          f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp],
         "tllm_attention_biased_decode": [vp, vp, vp, i64, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32,
-                                         f32, f32, i32, i32, i32, vp, vp, i32, i32, vp, vp, vp],
+                                         f32, f32, i32, i32, i32, vp, vp, i32, vp, i32, i32, vp, vp, vp],
+        "tllm_embedding_norm": [vp, vp, vp, vp, i32, vp, f32, f32, vp, i32, i32, i32, i32, vp],
+        "tllm_softcap": [vp, f32, i64, vp],
+        "tllm_stream_add": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
+        "tllm_activation": [vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp],
+        "tllm_delta_prepare": [vp, i32, i32, vp, i32, vp, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, f32,
+                               vp, vp, vp, vp, vp, i32, vp],
+        "tllm_delta_scan": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
+        "tllm_delta_finish": [vp, vp, i32, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64, vp],
+        "tllm_latent_norm_store": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, f32, vp, vp, vp, i32, i32,
+                                   vp, i64, vp, i32, i32, vp],
+        "tllm_latent_query": [vp, vp, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, vp],
+        "tllm_heads_gate": [vp, vp, i32, i32, i32, i32, i32, vp, vp, vp],
         "tllm_moe_route": [vp, i32, i32, i32, i32, vp, vp, vp],
         "tllm_moe_plan": [vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
         "tllm_moe_grouped": [vp, i32, vp, vp, i32, vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
@@ -103,6 +115,10 @@ def _declare(h) -> None:
         fn = getattr(h, name)
         fn.argtypes = args
         fn.restype = i32
+    h.tllm_delta_rule_lanes.argtypes = [i32]
+    h.tllm_delta_rule_lanes.restype = i32
+    h.tllm_delta_rule_state_floats.argtypes = [i32, i32, i32, i32, i32]
+    h.tllm_delta_rule_state_floats.restype = i64
     h.tllm_attention_biased_fast_ok.argtypes = [i32, i32, i32, i32]
     h.tllm_attention_biased_fast_ok.restype = i32
     h.tllm_moe_tile_rows.argtypes = []
@@ -636,17 +652,28 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
                      block_table, page_size: int, q_heads: int, kv_heads: int, dk: int, dv: int, scale: float,
                      out: torch.Tensor, softcap: float = 0.0, chunk: int = 0, window: int = 0,
                      sink: bool = False, slopes: Optional[torch.Tensor] = None,
-                     gate: Optional[torch.Tensor] = None, ctx=None) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, ctx=None, sink_logits: Optional[torch.Tensor] = None,
+                     values_in_keys: bool = False) -> torch.Tensor:
     """Attention of every row of ``q`` [T, q_heads * dk] over the keys of its own request, with the
     score s = (q . k) * scale changed in this order by whatever is given: ``softcap`` (s <- cap *
     tanh(s / cap)), ``slopes`` [q_heads] float32 (s <- s - slope * (pos - key pos)); keys j <= pos from
     the row's own ``chunk`` of positions and from its ``window``; ``sink``: one is added to the softmax's
-    denominator.  ``gate`` (a view [T, q_heads * dv] whose rows may be strided): out *= sigmoid(gate)."""
-    _cuda(q, positions, token_slot, block_table, out, slopes)
+    denominator, or exp(sink_logits[head]) with ``sink_logits`` [q_heads] float32 (a learned score that is
+    neither scaled nor capped).  ``gate`` (a view [T, q_heads * dv] whose rows may be strided): out *=
+    sigmoid(gate).  ``values_in_keys``: a value is the first ``dv`` elements of its key's row (``v_plane`` is
+    not looked at), as in attention over compressed vectors that are key and, in part, value at once."""
+    _cuda(q, positions, token_slot, block_table, out, slopes, sink_logits)
     tokens = q.shape[0]
     assert tuple(out.shape) == (tokens, q_heads * dv) and out.dtype == q.dtype
-    (kp, stride), (vp, stride_v) = _plane(k_plane), _plane(v_plane)
+    kp, stride = _plane(k_plane)
+    if values_in_keys:
+        assert dv <= dk
+        vp, stride_v, v_row = kp, stride, dk
+    else:
+        (vp, stride_v), v_row = _plane(v_plane), dv
     assert stride == stride_v and k_plane.dtype == q.dtype
+    if sink_logits is not None:
+        assert sink and sink_logits.dtype == torch.float32 and sink_logits.numel() == q_heads
     gate_stride = 0
     if gate is not None:
         assert gate.dtype == q.dtype and gate.stride(1) == 1 and tuple(gate.shape) == tuple(out.shape)
@@ -655,10 +682,10 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
         assert slopes.dtype == torch.float32 and slopes.numel() == q_heads
     gate_ptr = None if gate is None else gate.data_ptr()
     mods = (float(scale), float(softcap or 0.0), int(chunk or 0), int(window or 0), int(bool(sink)), _p(slopes),
-            gate_ptr, gate_stride)
+            _p(sink_logits), v_row, gate_ptr, gate_stride)
     consts = mods + (_p(out), _stream())
     if BIASED_FAST and ctx is not None and ctx.pf_tiles is not None and ctx.tokens == tokens \
-            and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 \
+            and q.dtype == torch.bfloat16 and gate_stride % 2 == 0 and v_row % 8 == 0 \
             and lib().tllm_attention_biased_fast_ok(q_heads, kv_heads, dk, dv):
         # one-token rows: keys read once per group of query heads; longer portions: tensor-core tiles
         if ctx.n_dec:
@@ -679,8 +706,162 @@ def attention_biased(q: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tens
     _check(lib().tllm_attention_biased_general(
         _p(q), kp, vp, stride, _p(positions), _p(token_slot), _p(block_table), block_table.shape[1], page_size,
         _dt(q), tokens, q_heads, kv_heads, dk, dv, float(scale), float(softcap or 0.0), int(chunk or 0),
-        int(window or 0), int(bool(sink)), _p(slopes), None if gate is None else gate.data_ptr(), gate_stride,
-        _p(out), _stream()), "attention_biased")
+        int(window or 0), int(bool(sink)), _p(slopes), _p(sink_logits), v_row,
+        None if gate is None else gate.data_ptr(), gate_stride, _p(out), _stream()), "attention_biased")
+    return out
+
+
+# --------------------------------------------------------------------------- stream, embedding with positions, activations
+ELEMENTWISE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}      # codes of csrc/common.cuh (GateAct)
+
+
+def embedding_norm(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+                   positions: Optional[torch.Tensor] = None, pos_table: Optional[torch.Tensor] = None,
+                   gain: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+    """out[t] = norm(table[ids[t]] * scale + pos_table[positions[t]]) in float32: the position table and the
+    norm (``gain`` float32, the factor itself; x / sqrt(mean(x^2) + eps) * gain) only where they are given."""
+    _cuda(ids, table, out, positions, pos_table, gain)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32
+    vocab, hidden = table.shape
+    if pos_table is not None:
+        assert pos_table.dtype == table.dtype and pos_table.shape[1] == hidden and positions.dtype == torch.int32
+    if gain is not None:
+        assert gain.dtype == torch.float32 and gain.numel() == hidden
+    _check(lib().tllm_embedding_norm(_p(ids), _p(positions), _p(table), _p(pos_table), _dt(table), _p(gain), float(eps),
+                                     float(scale), _p(out), ids.numel(), hidden, vocab,
+                                     0 if pos_table is None else pos_table.shape[0], _stream()), "embedding_norm")
+    return out
+
+
+def stream_add(h: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+               post_gain: Optional[torch.Tensor] = None, post_eps: float = 0.0) -> torch.Tensor:
+    """h += delta (float32, written back) and out = h in the storage type, with no norm on the way out.  With
+    ``post_gain`` the delta is normed first: h += post_gain * delta / sqrt(mean(delta^2) + post_eps)."""
+    _cuda(h, delta, out, post_gain)
+    assert h.dtype == torch.float32 and out.shape == h.shape
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape == h.shape
+    gdt = _dt(post_gain) if post_gain is not None else F32
+    _check(lib().tllm_stream_add(_p(h), _p(delta), _p(post_gain), gdt, float(post_eps), _p(out), _dt(out), h.shape[0],
+                                 h.shape[1], _stream()), "stream_add")
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place, float32."""
+    _cuda(x)
+    assert x.dtype == torch.float32
+    _check(lib().tllm_softcap(_p(x), float(cap), x.numel(), _stream()), "softcap")
+    return x
+
+
+def activation(x: torch.Tensor, act: str, ids: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None,
+               col0: int = 0) -> torch.Tensor:
+    """act(x) element by element (``silu``, ``gelu_tanh``, ``gelu_erf``; float32 inside); with ``table`` [vocab,
+    columns] and ``ids``, times table[ids[t], col0 + j]: a gate on a vector looked up by the row's token."""
+    _cuda(x, ids, table)
+    tokens, width = x.shape
+    out = torch.empty_like(x)
+    if table is not None:
+        assert table.dtype == x.dtype and ids.dtype == torch.int32 and ids.numel() == tokens
+    _check(lib().tllm_activation(_p(x), _p(out), _dt(x), ELEMENTWISE_ACTIVATIONS[act], tokens, width, _p(ids), _p(table),
+                                 0 if table is None else table.shape[1], int(col0),
+                                 0 if table is None else table.shape[0], _stream()), "activation")
+    return out
+
+
+# --------------------------------------------------------------------------- delta rule with channel-wise decay
+def delta_rule_state_floats(heads: int, kv_heads: int, dk: int, dv: int, taps: int) -> int:
+    """Float32 words of one request's state: S of every head in the scan kernel's layout, then the
+    convolution's last ``taps - 1`` inputs."""
+    return int(lib().tllm_delta_rule_state_floats(heads, kv_heads, dk, dv, taps))
+
+
+def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, a: torch.Tensor, dt_bias: torch.Tensor,
+               rate: torch.Tensor, gate: torch.Tensor, out_weight: torch.Tensor, eps: float, token_slot: torch.Tensor,
+               seg_info: Optional[torch.Tensor], state: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
+               q_scale: float, unit_eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """One step of the delta rule with a decay per head and key channel for every row of ``proj`` [T, >= channels
+    + heads] = q channels | k channels | v channels | beta logits (storage type): convolution with ``conv_w``
+    [channels, taps] and SiLU, unit q and k, g = exp(-rate_h softplus(a + dt_bias)) with ``a`` [T, heads * dk]
+    float32, the recurrence over each portion's rows from ``state[slot]`` (float32, updated in place), then the
+    read-out divided by its root mean square per head, times ``out_weight`` [dv] float32, times sigmoid(``gate``)
+    ([T, heads * dv] float32, rows may be strided).  ``seg_info`` [segments, 4] = slot, first row, length, first
+    position; None: every row is a portion of one token.  Returns [T, heads * dv] in ``out_dtype``."""
+    _cuda(proj, conv_w, dt_bias, rate, out_weight, token_slot, seg_info, state)
+    tokens, ld = proj.shape
+    assert a.dtype == gate.dtype == dt_bias.dtype == rate.dtype == out_weight.dtype == state.dtype == torch.float32
+    assert a.stride(1) == 1 and gate.stride(1) == 1 and conv_w.dtype == proj.dtype and state.dim() == 2
+    dev = proj.device
+    ws = workspace(dev, tokens * (2 * kv_heads * dk + 2 * heads * dv + heads * dk + heads))
+    at = 0
+
+    def take(n):
+        nonlocal at
+        t = ws[at:at + tokens * n]
+        at += tokens * n
+        return t
+    qn, kn, vv, decay, beta, o_raw = (take(kv_heads * dk), take(kv_heads * dk), take(heads * dv), take(heads * dk),
+                                      take(heads), take(heads * dv))
+    _check(lib().tllm_delta_prepare(_p(proj), ld, _dt(proj), _p(conv_w), taps, a.data_ptr(), a.stride(0), _p(dt_bias), _p(rate),
+                                    _p(token_slot), _p(state), state.stride(0), heads, kv_heads, dk, dv, float(q_scale),
+                                    float(unit_eps), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta), tokens, _stream()),
+           "delta_prepare")
+    segments = tokens if seg_info is None else seg_info.shape[0]
+    _check(lib().tllm_delta_scan(_p(seg_info), segments, _p(token_slot), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta),
+                                 _p(state), state.stride(0), heads, kv_heads, dk, dv, _p(o_raw), _stream()), "delta_scan")
+    out = torch.empty((tokens, heads * dv), dtype=out_dtype, device=dev)
+    _check(lib().tllm_delta_finish(_p(o_raw), gate.data_ptr(), gate.stride(0), _p(out_weight), float(eps), _p(token_slot),
+                                   tokens, heads, kv_heads, dk, dv, _p(out), _dt(out), _p(proj), ld, taps, _p(state),
+                                   state.stride(0), _stream()), "delta_finish")
+    return out
+
+
+# --------------------------------------------------------------------------- attention over compressed vectors
+def latent_norm_store(proj: torch.Tensor, q_rank: int, rank: int, rot: int, rot_dims: int, q_gain, c_gain,
+                      eps: float, freq: torch.Tensor, mag: float, positions, token_slot, block_table,
+                      plane: torch.Tensor, page_size: int, store: bool = True) -> Optional[torch.Tensor]:
+    """Rows of ``proj`` = query latent (q_rank) | key/value latent (rank) | shared key part (rot) | anything.
+    Returns the query latent divided by its root mean square times ``q_gain`` (None if q_rank is 0) and
+    writes [normed latent times ``c_gain`` | rotated key part] of every row into its place of ``plane``
+    ([pages, 1, page, rank + rot]).  Gains and ``freq`` [rot_dims / 2] are float32."""
+    _cuda(proj, q_gain, c_gain, freq, positions, token_slot, block_table)
+    tokens = proj.shape[0]
+    cq = torch.empty((tokens, q_rank), dtype=proj.dtype, device=proj.device) if q_rank else None
+    pp, stride = _plane(plane)
+    assert plane.dtype == proj.dtype and tuple(plane.shape[1:]) == (1, page_size, rank + rot)
+    _check(lib().tllm_latent_norm_store(_p(proj), proj.shape[1], _dt(proj), q_rank, rank, rot, rot_dims, _p(q_gain),
+                                        _p(c_gain), float(eps), _p(freq), float(mag), _p(positions), _p(token_slot),
+                                        _p(block_table), block_table.shape[1], page_size, pp, stride, _p(cq), int(store),
+                                        tokens, _stream()), "latent_norm_store")
+    return cq
+
+
+def latent_query(q: torch.Tensor, lat: torch.Tensor, heads: int, plain: int, rot: int, rot_dims: int, rank: int,
+                 freq: torch.Tensor, mag: float, positions, token_slot) -> torch.Tensor:
+    """[T, heads, rank + rot]: per head ``lat`` [heads, T, rank] followed by the rotated last ``rot`` elements
+    of the head's query in ``q`` [T, heads * (plain + rot)]."""
+    _cuda(q, lat, freq, positions, token_slot)
+    tokens = q.shape[0]
+    assert tuple(lat.shape) == (heads, tokens, rank) and lat.dtype == q.dtype and q.shape[1] == heads * (plain + rot)
+    out = torch.empty((tokens, heads * (rank + rot)), dtype=q.dtype, device=q.device)
+    _check(lib().tllm_latent_query(_p(q), _p(lat), _dt(q), heads, plain, rot, rot_dims, rank, _p(freq), float(mag),
+                                   _p(positions), _p(token_slot), tokens, _p(out), _stream()), "latent_query")
+    return out
+
+
+def heads_gate(x: torch.Tensor, gate: Optional[torch.Tensor], token_slot=None) -> torch.Tensor:
+    """[T, heads * width] = x[h, t, :] * sigmoid(gate[t, h * width + :]) for ``x`` [heads, T, width]; ``gate`` is a
+    view whose rows may be strided (None: no gate)."""
+    _cuda(x, token_slot)
+    heads, tokens, width = x.shape
+    out = torch.empty((tokens, heads * width), dtype=x.dtype, device=x.device)
+    ldg = 0
+    if gate is not None:
+        assert gate.dtype == x.dtype and gate.stride(1) == 1 and tuple(gate.shape) == (tokens, heads * width)
+        ldg = gate.stride(0)
+    _check(lib().tllm_heads_gate(_p(x), None if gate is None else gate.data_ptr(), ldg, _dt(x), heads, width, tokens,
+                                 _p(token_slot), _p(out), _stream()), "heads_gate")
     return out
 
 

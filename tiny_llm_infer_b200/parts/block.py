@@ -10,6 +10,13 @@ h += norm2b(ffn(norm2(h))).  The output norms are not run on their own: the sub-
 on as a ``NormedDelta`` and the next norm kernel (this layer's norm2, the next layer's norm1, or
 the model's last norm) norms it, adds it and norms the sum.  ``sandwich_mixer`` is the same layer
 without a feed-forward.
+
+``stream_*``: the sub-layers read the residual stream itself, and only their outputs are normed:
+h += norm1(mixer(h)), then h += norm2(ffn(h)), then h += norm3(side(h)), where the feed-forward and the
+side input (a feed-forward that also looks at the step's tokens) are each there or not: ``stream_mixer``,
+``stream_mixer_ffn``, ``stream_mixer_side``, ``stream_mixer_ffn_side``.  Every sum is one kernel that norms the
+output, adds it in float32 and hands the stream on in the storage type; the last output goes on as a
+``NormedDelta`` like the sandwich's.
 """
 from __future__ import annotations
 
@@ -17,6 +24,8 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .. import ops
+from .norm import NormedDelta
 from .registry import register
 
 
@@ -70,3 +79,38 @@ class SandwichMixerBlock(Block):
     def forward(self, h: torch.Tensor, pending, ctx, cache):
         x = self.norm1.forward(h, pending)
         return self.norm1b.wrap(self.mixer.forward(x, ctx, cache))
+
+
+def _stream(h: torch.Tensor, pending, dtype: torch.dtype) -> torch.Tensor:
+    """h += pending (normed first if it is a ``NormedDelta``); the stream in the storage type."""
+    out = torch.empty(h.shape, dtype=dtype, device=h.device)
+    if isinstance(pending, NormedDelta):
+        return ops.stream_add(h, pending.delta, out, post_gain=pending.gain, post_eps=pending.eps)
+    return ops.stream_add(h, pending, out)
+
+
+def _stream_block(name: str, with_ffn: bool, with_side: bool) -> type:
+    roles = {"mixer": "mixer", "norm1": "norm"}
+    if with_ffn:
+        roles.update({"ffn": "feed_forward", "norm2": "norm"})
+    if with_side:
+        roles.update({"side": "feed_forward", "norm3": "norm"})
+
+    class StreamBlock(Block):
+        def forward(self, h: torch.Tensor, pending, ctx, cache):
+            dtype = self.norm1.dtype
+            pending = self.norm1.wrap(self.mixer.forward(_stream(h, pending, dtype), ctx, cache))
+            if with_ffn:
+                pending = self.norm2.wrap(self.ffn.forward(_stream(h, pending, dtype), ctx))
+            if with_side:
+                pending = self.norm3.wrap(self.side.forward(_stream(h, pending, dtype), ctx))
+            return pending
+
+    StreamBlock.roles = roles
+    StreamBlock.__name__ = StreamBlock.__qualname__ = "".join(w.title() for w in name.split("_")) + "Block"
+    return register("block", name)(StreamBlock)
+
+
+for _ffn in (False, True):
+    for _side in (False, True):
+        _stream_block("stream_mixer" + ("_ffn" if _ffn else "") + ("_side" if _side else ""), _ffn, _side)

@@ -55,3 +55,67 @@ class SwiGLUFeedForward:
         act = ops.linear_swiglu(x, self.w_gate_up, out_dtype=self.dtype, interleaved=self.interleaved,
                                 act=self.activation)
         return ops.linear(act, self.w_down, out_dtype=self.dtype)
+
+
+@register("feed_forward", "mlp")
+class PlainFeedForward:
+    """d = act(x Wu^T) Wd^T, no gate and no biases; ``activation`` is ``gelu_erf`` (the exact GELU,
+    0.5 z (1 + erf(z / sqrt 2))), ``gelu_tanh`` or ``silu``, computed in float32."""
+    NAMES = ("up", "down")
+
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype: torch.dtype, device,
+                 activation: str = "gelu_erf", names=NAMES):
+        if activation not in ops.ELEMENTWISE_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ELEMENTWISE_ACTIVATIONS)}")
+        self.hidden, self.inter, self.dtype, self.device = hidden_size, intermediate_size, dtype, device
+        self.activation, self.names = activation, tuple(names)
+        self.w_up = self.w_down = None
+
+    @classmethod
+    def param_specs(cls, hidden_size, intermediate_size, activation: str = "gelu_erf", names=NAMES) -> Dict[str, ParamSpec]:
+        up, down = names
+        return {up: ParamSpec((intermediate_size, hidden_size)), down: ParamSpec((hidden_size, intermediate_size))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = t[self.names[0]].contiguous(), t[self.names[1]].contiguous()
+
+    def workspace_floats(self, tokens: int) -> int:
+        return 2 * tokens * self.inter
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        z = ops.linear(x, self.w_up, out_dtype=self.dtype)
+        return ops.linear(ops.activation(z, self.activation), self.w_down, out_dtype=self.dtype)
+
+
+@register("feed_forward", "token_side")
+class TokenSideInput:
+    """A small input per layer that depends on the row's token: e = table[token, first_column : first_column +
+    side_dim]; d = (act(x Wg^T) * e) Wp^T.  The table belongs to the embedding, which publishes it in the
+    step's memo under ``memo_key`` (all layers share it and read their own columns); the look-up, the
+    activation and the product with e are one kernel."""
+    NAMES = ("gate", "proj")
+
+    def __init__(self, hidden_size: int, side_dim: int, first_column: int, dtype: torch.dtype, device,
+                 activation: str = "gelu_tanh", memo_key: str = "token_side_table", names=NAMES):
+        if activation not in ops.ELEMENTWISE_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ELEMENTWISE_ACTIVATIONS)}")
+        self.hidden, self.side_dim, self.first_column = hidden_size, int(side_dim), int(first_column)
+        self.dtype, self.device, self.activation, self.memo_key, self.names = dtype, device, activation, memo_key, tuple(names)
+        self.w_gate = self.w_proj = None
+
+    @classmethod
+    def param_specs(cls, hidden_size, side_dim, first_column=0, activation: str = "gelu_tanh",
+                    memo_key: str = "token_side_table", names=NAMES) -> Dict[str, ParamSpec]:
+        gate, proj = names
+        return {gate: ParamSpec((side_dim, hidden_size)), proj: ParamSpec((hidden_size, side_dim))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_gate, self.w_proj = t[self.names[0]].contiguous(), t[self.names[1]].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        table = ctx.memo.get(self.memo_key)
+        if table is None:
+            raise ValueError(f"no table under {self.memo_key!r} in the step's memo: the embedding has to publish it")
+        z = ops.linear(x, self.w_gate, out_dtype=self.dtype)
+        g = ops.activation(z, self.activation, ids=ctx.token_ids, table=table, col0=self.first_column)
+        return ops.linear(g, self.w_proj, out_dtype=self.dtype)

@@ -6,6 +6,10 @@ reference adds the residual in a separate half-precision kernel
 (model/src/qwen3_paged_batch.cpp:273-279); here the sum is float32 and happens in the
 same pass that computes the norm.
 
+``offset``: the checkpoint stores the gain minus this number (a weight "around zero" has offset 1); the
+sum gain = offset + stored weight is made once at load, in float32, and kept in float32.  ``float32_gain``
+keeps a plain gain in float32 too (a model whose other norms do, so that one kernel sees one gain type).
+
 A block that norms a sub-layer's output before the residual sum hands that output on as a
 ``NormedDelta`` (``wrap``): the norm that follows takes it as its ``delta`` and does the output's norm,
 the sum and its own norm in one kernel, h += g_post * d / sqrt(mean(d^2) + eps_post) in float32.
@@ -33,18 +37,23 @@ class NormedDelta:
 
 @register("norm", "rmsnorm")
 class RMSNorm:
-    def __init__(self, width: int, eps: float, dtype: torch.dtype, device, name: str = "weight"):
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device, name: str = "weight",
+                 offset: float = 0.0, float32_gain: bool = False):
         self.width, self.eps, self.dtype, self.device = int(width), float(eps), dtype, device
-        self.name = name
+        self.name, self.offset, self.float32_gain = name, float(offset), bool(float32_gain)
         self.gain: Optional[torch.Tensor] = None
 
     @classmethod
-    def param_specs(cls, width: int, eps: float, name: str = "weight") -> Dict[str, ParamSpec]:
+    def param_specs(cls, width: int, eps: float, name: str = "weight", offset: float = 0.0,
+                    float32_gain: bool = False) -> Dict[str, ParamSpec]:
         """``name``: what the gain is called behind the part's prefix in the checkpoint."""
-        return {name: ParamSpec((int(width),), "norm")}
+        return {name: ParamSpec((int(width),), "norm_zero" if offset else "norm")}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.gain = tensors[self.name].contiguous()
+        gain = tensors[self.name]
+        if self.offset or self.float32_gain:
+            gain = gain.to(torch.float32) + self.offset
+        self.gain = gain.contiguous()
 
     def wrap(self, delta: torch.Tensor) -> NormedDelta:
         """``delta`` with this norm still to be applied to it, by the norm that adds it to the stream."""

@@ -16,7 +16,8 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 @dataclass(frozen=True)
 class ParamSpec:
     """One tensor a part owns.  ``init`` is what random-weights mode fills it with:
-    ``normal`` (matrices, embeddings), ``norm`` (norm gains, uniform in a range) or
+    ``normal`` (matrices, embeddings), ``norm`` (norm gains, uniform in a range), ``norm_zero`` (gains
+    stored as their distance from one), ``unit`` (numbers of order one: rates, biases, learned scores) or
     ``index`` (integer tables, kept as int32)."""
     shape: Tuple[int, ...]
     init: str = "normal"

@@ -76,15 +76,19 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, std: float, norm_range:
     count = math.prod(spec.shape) if spec.shape else 1
     if spec.init == "index":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
-    if spec.init not in ("norm", "normal"):
+    if spec.init not in ("norm", "norm_zero", "normal", "unit"):
         raise ValueError(f"{name}: unknown init {spec.init!r}")
     out = torch.empty(count, dtype=dtype, device=device)
     slab = 1 << 24                                       # elements made at a time (float64 and int64 temporaries)
     for start in range(0, count, slab):
         n = min(slab, count - start)
-        if spec.init == "norm":
+        if spec.init in ("norm", "norm_zero"):
             lo, hi = norm_range
             values = _uniform(key, start, n, device) * (hi - lo) + lo
+            if spec.init == "norm_zero":                 # a gain stored as its distance from one
+                values = values - 1.0
+        elif spec.init == "unit":                        # numbers of order one whatever the matrices' spread
+            values = _normal(key, start, n, device) * 0.5   # (rates, biases and scores that enter an exponential)
         else:
             values = _normal(key, start, n, device) * std
         out[start:start + n] = values.to(torch.float32).to(dtype)

@@ -128,6 +128,18 @@ def checkpoint_files(model_path) -> List[Path]:
     raise SafetensorsError(f"{path}: neither model.safetensors nor model.safetensors.index.json")
 
 
+def tensor_shapes(model_path) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape of every tensor of a model folder, from the files' headers alone."""
+    out: Dict[str, Tuple[int, ...]] = {}
+    for path in checkpoint_files(model_path):
+        f = SafetensorsFile(path)
+        try:
+            out.update({name: tuple(info.shape) for name, info in f.tensors.items()})
+        finally:
+            f.close()
+    return out
+
+
 def save_file(tensors: Dict[str, torch.Tensor], path, metadata: Dict[str, str] = None) -> None:
     """Write tensors (CPU) to one .safetensors file, in name order, 8-byte aligned header."""
     header: Dict[str, object] = {}
