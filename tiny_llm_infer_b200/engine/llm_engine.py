@@ -266,7 +266,14 @@ def estimate_num_kv_blocks(model, block_size: int, dtype: torch.dtype, max_num_b
     per_page = sum(CacheManager.bytes_per_page(model.cache_needs(), block_size, dtype).values())
     workspace = 4 * model.workspace_floats(max_num_batched_tokens, min(max_num_seqs, max_num_batched_tokens))
     reserve = max(256 << 20, total // 20, workspace)
-    budget = int(total * gpu_memory_utilization) - used - reserve
+    states = 0                                   # fixed-size state of every mixer that keeps one, per request slot
+    for _, state in model.cache_needs().values():
+        if state is not None:
+            size = torch.empty((), dtype=getattr(torch, state.dtype)).element_size()
+            for n in state.shape:
+                size *= int(n)
+            states += size * max_num_seqs
+    budget = int(total * gpu_memory_utilization) - used - reserve - states
     return max(0, budget // max(per_page, 1))
 
 

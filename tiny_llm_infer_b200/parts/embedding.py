@@ -43,7 +43,8 @@ class TokenEmbedding:
 class TokenPositionEmbedding:
     """h0[t] = norm(E[token[t]] * scale + P[position[t]]): a learned vector per position (``max_positions``
     rows, not scaled) and, if ``norm_eps`` is given, an RMS norm of the sum with the gain ``norm_offset`` +
-    stored weight, all in float32 in one kernel.  A position past the table is an error of the step.
+    stored weight, all in float32 in one kernel.  The engine bounds a request's length by the model's
+    ``max_positions`` (the cache manager refuses to reserve beyond it), so no row comes with a position past the table.
 
     ``side_columns`` > 0 adds a second table [vocab, side_columns] (``side_name``) that this part owns and
     layers look rows up in by the step's token ids (a per-layer input that depends on the token alone); it is
@@ -83,8 +84,6 @@ class TokenPositionEmbedding:
     def forward(self, token_ids: torch.Tensor, ctx=None) -> torch.Tensor:
         if ctx is None:
             raise ValueError("an embedding with positions needs the step's context")
-        if ctx.max_context > self.max_positions:
-            raise ValueError(f"position {ctx.max_context - 1} is past the {self.max_positions} learned positions")
         if self.side is not None:
             ctx.memo[self.TOKEN_SIDE] = self.side
         h = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
