@@ -409,40 +409,33 @@ DESIGN_SIZES = {
 }
 
 
-def design_bench(args) -> int:
-    """``--design panolorn``: prefill and decode throughput of the Panolorn design at sizes that resemble a
-    real model's layers (random weights, bfloat16; layers alternate dense and mixture feed-forwards), beside
-    Qwen3 dense, the closest model the engine has, at equal sizes (same width, heads, head width, layers,
-    vocabulary, and a feed-forward as wide as a token's share of the mixture), through the same step
-    function; and the new kernels one by one beside their relatives, with their share of the measured
-    peaks.  One JSON line."""
-    import math
-    import torch
-    from tiny_llm_infer_b200 import ops
-    from tiny_llm_infer_b200.cache import CacheManager
-    from tiny_llm_infer_b200.config import Qwen3Config
-    from tiny_llm_infer_b200.config.panolorn import (AttentionMixerConfig, FeedForwardConfig, PanolornConfig,
-                                                      PanolornLayerConfig)
-    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, random_model
+class _DesignHarness:
+    """What the ``--design`` benches share: the timing of one call (three warm-up calls, then the median of
+    ``reps`` calls with L2 flushed before each, CUDA events on the launching stream) and a model's prefill and
+    decode through the engine's step function."""
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
-    device = "cuda:0"
-    pk = peaks()
-    ops.lib()
-    gen = torch.Generator().manual_seed(0)
-    clocks = ClockSampler()
-    clocks.start()
-    windows = []
-    tokens_pf, batch, context = 2048, args.batch, 2048
-    steps, warmup = max(4, min(args.steps, 32)), max(args.warmup, 3)
-    flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)      # larger than L2
+    def __init__(self, args):
+        import torch
+        from tiny_llm_infer_b200 import ops
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+        self.device = "cuda:0"
+        self.pk = peaks()
+        ops.lib()
+        self.gen = torch.Generator().manual_seed(0)
+        self.clocks = ClockSampler()
+        self.clocks.start()
+        self.windows = []
+        self.tokens_pf, self.batch, self.context = 2048, args.batch, 2048
+        self.steps, self.warmup = max(4, min(args.steps, 32)), max(args.warmup, 3)
+        self.flush = torch.empty(160 << 20, dtype=torch.uint8, device=self.device)      # larger than L2
 
-    def timed(fn, reps=5):
+    def timed(self, fn, reps=5):
+        import torch
         for _ in range(3):
             fn()
         out = []
         for _ in range(reps):
-            flush.zero_()
+            self.flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             a.record()
@@ -452,7 +445,16 @@ def design_bench(args) -> int:
             out.append(a.elapsed_time(b))
         return statistics.median(out)
 
-    def run_model(cfg, name, params, kv_bytes_per_token):
+    def run_model(self, cfg, name, params, kv_bytes_per_token, state_bytes_per_request=0):
+        """``params``: weights a prefill multiplies with per token (``active``) and weights a decode step reads
+        (``read``); ``kv_bytes_per_token``: cache bytes a decode row reads per token of its context;
+        ``state_bytes_per_request``: fixed-size state a decode row reads and writes."""
+        import torch
+        from tiny_llm_infer_b200 import ops
+        from tiny_llm_infer_b200.cache import CacheManager
+        from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, random_model
+        device, gen, batch, context, tokens_pf = self.device, self.gen, self.batch, self.context, self.tokens_pf
+        steps, warmup, windows, timed = self.steps, self.warmup, self.windows, self.timed
         model = random_model(cfg, seed=0, dtype=torch.bfloat16, device=device, std=0.02)
         page = 16
         pages = (batch + 1) * (context // page) + 2 * (tokens_pf // page) + 64
@@ -497,14 +499,37 @@ def design_bench(args) -> int:
         for n in names:
             runner.release(n)
         runner.check_kernels()
+        moved = 2.0 * params["read"] + batch * (context * kv_bytes_per_token + 2 * state_bytes_per_request)
         out = {"prefill_tokens_per_s": round(tokens_pf / pf_ms * 1e3, 1), "prefill_ms": round(pf_ms, 3),
                "prefill_tflops": round(2.0 * tokens_pf * params["active"] / pf_ms / 1e9, 1),
                "decode_tokens_per_s": round(batch / dec_ms * 1e3, 1), "decode_ms": round(dec_ms, 4),
-               "decode_gbs": round((2.0 * params["read"] + batch * context * kv_bytes_per_token) / dec_ms / 1e6, 1),
+               "decode_gbs": round(moved / dec_ms / 1e6, 1),
                "launches_per_decode_step": launches // max(steps, 1)}
         del runner, cache, model
         torch.cuda.empty_cache()
         return out
+
+
+def design_bench(args) -> int:
+    """``--design panolorn``: prefill and decode throughput of the Panolorn design at sizes that resemble a
+    real model's layers (random weights, bfloat16; layers alternate dense and mixture feed-forwards), beside
+    Qwen3 dense, the closest model the engine has, at equal sizes (same width, heads, head width, layers,
+    vocabulary, and a feed-forward as wide as a token's share of the mixture), through the same step
+    function; and the new kernels one by one beside their relatives, with their share of the measured
+    peaks.  One JSON line."""
+    import math
+    import torch
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.cache import CacheManager
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.config.panolorn import (AttentionMixerConfig, FeedForwardConfig, PanolornConfig,
+                                                      PanolornLayerConfig)
+    from tiny_llm_infer_b200.engine import ModelRunner, StepEntry, random_model
+
+    hx = _DesignHarness(args)
+    device, pk, gen, clocks, windows = hx.device, hx.pk, hx.gen, hx.clocks, hx.windows
+    tokens_pf, batch, context, steps, warmup = hx.tokens_pf, hx.batch, hx.context, hx.steps, hx.warmup
+    timed, run_model = hx.timed, hx.run_model
 
     record = {"sizes": {}}
     for size_name in ([args.model] if args.model in DESIGN_SIZES else sorted(DESIGN_SIZES)):
@@ -664,6 +689,204 @@ def design_bench(args) -> int:
     return 0
 
 
+KAKETAR_SIZES = {
+    # width, layers (every fourth one latent attention, the others the delta rule), feed-forward on every layer;
+    # delta rule: heads, key and value width, taps, low ranks; latent attention: heads, unrotated / rotated / value
+    # width, the two latents (cached vector = kv_rank + rot = 128, the widest the tensor-core tiles take), window
+    "1b": dict(width=2048, layers=8, ff=6144, vocab=32768, side=64, d_heads=16, d_dim=128, d_vdim=128, taps=4, rank=64,
+               a_heads=16, a_dim=64, a_rot=32, a_vdim=128, q_rank=512, kv_rank=96, window=1024),
+    "8b": dict(width=4096, layers=4, ff=12288, vocab=32768, side=64, d_heads=32, d_dim=128, d_vdim=128, taps=4, rank=128,
+               a_heads=32, a_dim=64, a_rot=32, a_vdim=128, q_rank=1024, kv_rank=96, window=1024),
+}
+
+
+def kaketar_bench(args) -> int:
+    """``--design kaketar``: prefill and decode throughput of the Kaketar design at sizes that resemble a real
+    model's layers (random weights, bfloat16; three delta-rule layers to one of latent attention, a feed-forward
+    and the token side input on every layer), beside Qwen3 dense, the closest model the engine has, at equal
+    sizes (same width, layers, head count and width of the delta rule's heads, feed-forward, vocabulary),
+    through the same step function; and the new kernels one by one beside their relatives, with their share of
+    the measured peaks.  One JSON line."""
+    import math
+    import torch
+    from tiny_llm_infer_b200 import ops
+    from tiny_llm_infer_b200.config import Qwen3Config
+    from tiny_llm_infer_b200.config.kaketar import (ChannelDeltaConfig, DenseConfig, KaketarConfig, KaketarLayerConfig,
+                                                     LatentAttentionConfig, RotationScaling)
+    from tiny_llm_infer_b200.engine.batch import StepContext
+    from tiny_llm_infer_b200.parts.delta_rule import state_floats
+
+    hx = _DesignHarness(args)
+    device, pk, clocks, windows = hx.device, hx.pk, hx.clocks, hx.windows
+    tokens_pf, batch, context, steps, warmup = hx.tokens_pf, hx.batch, hx.context, hx.steps, hx.warmup
+    timed, run_model = hx.timed, hx.run_model
+    record = {"sizes": {}}
+    for size_name in ([args.model] if args.model in KAKETAR_SIZES else sorted(KAKETAR_SIZES)):
+        z = KAKETAR_SIZES[size_name]
+        L, W = z["layers"], z["width"]
+        dmix = ChannelDeltaConfig(z["d_heads"], z["d_heads"], z["d_dim"], z["d_vdim"], z["taps"], z["rank"], z["rank"])
+        amix = LatentAttentionConfig(z["a_heads"], z["a_dim"], z["a_rot"], z["a_vdim"], z["q_rank"], z["kv_rank"],
+                                     1.0 / math.sqrt(z["a_dim"] + z["a_rot"]), 10000.0, z["a_rot"], z["window"],
+                                     RotationScaling(4.0, 1024.0, 32.0, 1.0))
+        kcfg = KaketarConfig(vocab=z["vocab"], width=W, max_positions=4096, embedding_scale=1.0, norm_eps=1e-6, layers=tuple(
+            KaketarLayerConfig("latent_attention", amix, DenseConfig(z["ff"])) if i % 4 == 3 else
+            KaketarLayerConfig("channel_delta", dmix, DenseConfig(z["ff"])) for i in range(L)),
+            logit_softcap=30.0, side_dim=z["side"])
+        H, D = z["d_heads"], z["d_dim"]
+        qcfg = Qwen3Config(hidden_size=W, intermediate_size=z["ff"], num_hidden_layers=L, num_attention_heads=H,
+                           num_key_value_heads=max(H // 4, 1), head_dim=D, vocab_size=z["vocab"], max_position_embeddings=8192,
+                           tie_word_embeddings=True, layer_types=("full_attention",) * L)
+        n_lat = L // 4
+        n_delta = L - n_lat
+        hd, hv = z["d_heads"] * z["d_dim"], z["d_heads"] * z["d_vdim"]
+        delta_w = W * (2 * hd + hv + z["d_heads"]) + 2 * W * z["rank"] + z["rank"] * (hd + hv) + hv * W
+        ah = z["a_heads"]
+        latent_w = W * (z["q_rank"] + z["kv_rank"] + z["a_rot"] + ah * z["a_vdim"]) + z["q_rank"] * ah * (z["a_dim"] + z["a_rot"]) \
+            + ah * z["kv_rank"] * (z["a_dim"] + z["a_vdim"]) + ah * z["a_vdim"] * W
+        side_w = 2 * W * z["side"]
+        k_params = n_delta * delta_w + n_lat * latent_w + L * (2 * W * z["ff"] + side_w) + z["vocab"] * W
+        G = max(H // 4, 1)
+        q_params = L * (W * (H + 2 * G) * D + H * D * W + 3 * W * z["ff"]) + z["vocab"] * W
+        state = 4 * n_delta * state_floats(z["d_heads"], z["d_heads"], z["d_dim"], z["d_vdim"], z["taps"])
+        k_kv = 2 * n_lat * (z["kv_rank"] + z["a_rot"]) * min(z["window"], context) / context
+        print(f"[bench] design sizes {size_name}: Kaketar", file=sys.stderr, flush=True)
+        ours = run_model(kcfg, f"kaketar {size_name}", {"active": k_params, "read": k_params}, k_kv, state)
+        print(f"[bench] {ours}\n[bench] design sizes {size_name}: Qwen3 dense", file=sys.stderr, flush=True)
+        theirs = run_model(qcfg, f"qwen3 {size_name}", {"active": q_params, "read": q_params}, 2 * G * D * 2 * L)
+        print(f"[bench] {theirs}", file=sys.stderr, flush=True)
+        for r in (ours, theirs):
+            r["prefill_frac_of_measured"] = round(r["prefill_tflops"] / pk["bf16_tflops"], 4)
+            r["decode_hbm_frac_of_measured"] = round(r["decode_gbs"] / pk["hbm_gbs"], 4)
+        record["sizes"][size_name] = {"kaketar": ours, "qwen3_dense": theirs, "config": z,
+                                      "params": {"kaketar": k_params, "qwen3_dense": q_params}}
+
+    # ---- kernels one by one at the larger sizes (L2 flushed between runs)
+    z = KAKETAR_SIZES["8b"]
+    W, bf, T = z["width"], torch.bfloat16, tokens_pf
+    kern = {}
+
+    def hbm(nbytes, ms):
+        return {"us": round(ms * 1e3, 1), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)}
+
+    def tensor(flops, ms):
+        return {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1), "frac_tensor": round(flops / ms / 1e9 / pk["bf16_tflops"], 3)}
+
+    # the sum of a normed output that hands the stream on without a norm, beside the sum + norm of the other blocks
+    h = torch.randn(T * 4, W, device=device)
+    delta = torch.randn(T * 4, W, device=device).to(bf)
+    gain32, gain16 = torch.ones(W, device=device), torch.ones(W, device=device, dtype=bf)
+    out = torch.empty_like(delta)
+    nbytes = h.numel() * 8 + delta.numel() * 4
+    kern["stream_add_normed_delta"] = hbm(nbytes, timed(lambda: ops.stream_add(h, delta, out, post_gain=gain32, post_eps=1e-6)))
+    kern["postnorm_add_rmsnorm"] = hbm(nbytes, timed(lambda: ops.add_rmsnorm(h, delta, gain16, 1e-6, out, post_gain=gain16, post_eps=1e-6)))
+    kern["add_rmsnorm"] = hbm(nbytes, timed(lambda: ops.add_rmsnorm(h, delta, gain16, 1e-6, out)))
+    del h, delta, out
+    # embedding + position + norm beside the plain look-up
+    table = torch.randn(z["vocab"], W, device=device).to(bf)
+    pos_table = torch.randn(4096, W, device=device).to(bf)
+    ids = torch.randint(0, z["vocab"], (T * 4,), device=device, dtype=torch.int32)
+    positions = (torch.arange(T * 4, device=device, dtype=torch.int32) % 4096).contiguous()
+    out32 = torch.empty(T * 4, W, device=device)
+    kern["embedding_position_norm"] = hbm(T * 4 * W * (2 + 2 + 4), timed(lambda: ops.embedding_norm(ids, table, out32, 2.0, positions, pos_table, gain32, 1e-6)))
+    kern["embedding"] = hbm(T * 4 * W * (2 + 4), timed(lambda: ops.embedding(ids, table, out32)))
+    del table, pos_table, out32
+    # activation of the plain feed-forward beside the gated one's
+    x = torch.randn(T, z["ff"], device=device).to(bf)
+    x2 = torch.randn(T, 2 * z["ff"], device=device).to(bf)
+    o = torch.empty_like(x)
+    kern["activation_gelu_erf"] = hbm(x.numel() * 4, timed(lambda: ops.activation(x, "gelu_erf")))
+    kern["swiglu"] = hbm(x.numel() * 6, timed(lambda: ops.swiglu(x2, o)))
+    del x, x2, o
+
+    # the delta rule: 2048 tokens of one request, and 64 one-token rows (state read and written once per row)
+    Hd, dk, dv, taps = z["d_heads"], z["d_dim"], z["d_vdim"], z["taps"]
+    channels = 2 * Hd * dk + Hd * dv
+    floats = state_floats(Hd, Hd, dk, dv, taps)
+    rows = 64
+    state = torch.zeros(rows, floats, device=device)
+    conv_w = (torch.randn(channels, taps, device=device) * 0.5).to(bf)
+    dt_bias = torch.randn(Hd * dk, device=device) - 4.0
+    rate = torch.ones(Hd, device=device)
+    weight = torch.ones(dv, device=device)
+    for what, n, seg in (("prefill_2048", T, [[0, 0, T, 0]]), ("decode_64_rows", rows, None)):
+        proj = torch.randn(n, channels + Hd, device=device).to(bf)
+        a = torch.randn(n, Hd * dk, device=device)
+        gate = torch.randn(n, Hd * dv, device=device)
+        slots = torch.zeros(n, dtype=torch.int32, device=device) if seg else torch.arange(n, dtype=torch.int32, device=device)
+        seg_info = torch.tensor(seg, dtype=torch.int32, device=device) if seg else None
+        ms = timed(lambda: ops.delta_rule(proj, conv_w, taps, a, dt_bias, rate, gate, weight, 1e-6, slots, seg_info, state,
+                                          Hd, Hd, dk, dv, dk ** -0.5, 1e-6, bf))
+        flops = 6.0 * n * Hd * dk * dv                      # decay and two rank-one steps per element of S, a read-out
+        io = n * ((channels + Hd) * 2 + (Hd * dk + Hd * dv) * 4 + Hd * dv * 2) + (0 if seg else 2 * rows * Hd * dk * dv * 4)
+        work = n * (2 * Hd * dk + 2 * Hd * dv + Hd * dk + Hd) * 4 * 2      # the float32 hand-over between the three kernels
+        kern[f"delta_rule_{what}"] = {"us": round(ms * 1e3, 1), "tokens_per_s": round(n / ms * 1e3, 1),
+                                      "gflops_fp32": round(flops / ms / 1e6, 1), "gbs": round((io + work) / ms / 1e6, 1),
+                                      "frac_hbm": round((io + work) / ms / 1e6 / pk["hbm_gbs"], 3)}
+    del state
+
+    # attention: cached latents (multi-query, values inside the keys) beside Qwen3's paged attention at the same
+    # head count; a prompt of 2048 tokens, and 64 one-token rows at context 2048 (the latents' window is 1024)
+    page, ctx_len = 16, context
+    n_pages = rows * ctx_len // page
+    table = torch.arange(n_pages, dtype=torch.int32, device=device).view(rows, ctx_len // page).contiguous()
+
+    def context_for(segs):
+        seg, tiles, dec, row = [], [], [], 0
+        for s, (slot, p0, n) in enumerate(segs):
+            seg.append([slot, row, n, p0])
+            if n == 1:
+                dec.append(row)
+            else:
+                tiles += [(s, off) for off in range(0, n, 64)]
+            row += n
+        tiles.sort(key=lambda t: (t[1] % 256 != 0, t[1] % 128 != 0))
+        pos = torch.tensor([p0 + i for _, p0, n in segs for i in range(n)], dtype=torch.int32, device=device)
+        slot = torch.tensor([sl for sl, _, n in segs for _ in range(n)], dtype=torch.int32, device=device)
+        return StepContext(tokens=row, token_ids=None, positions=pos, token_slot=slot, want_rows=None, segments=[],
+                           seg_info=torch.tensor(seg, dtype=torch.int32, device=device),
+                           dec_rows=None if len(dec) == row else torch.tensor(dec, dtype=torch.int32, device=device),
+                           n_dec=len(dec), pf_tiles=torch.tensor(tiles, dtype=torch.int32, device=device).view(-1, 2),
+                           n_tiles=len(tiles), n_tiles128=sum(1 for t in tiles if t[1] % 128 == 0),
+                           n_tiles256=sum(1 for t in tiles if t[1] % 256 == 0), max_context=ctx_len, max_segment=max(n for _, _, n in segs))
+
+    Ha, rank, rot, window = z["a_heads"], z["kv_rank"], z["a_rot"], z["window"]
+    wide = rank + rot
+    plane = (torch.randn(n_pages, 1, page, wide, device=device) * 0.5).to(bf)
+    sink = torch.zeros(Ha, device=device)
+    G, D = max(Ha // 4, 1), 128
+    kv_u = (torch.randn(n_pages, 2, G, page, D, device=device) * 0.5).to(bf)
+    for what, segs in (("prefill_2048", [(0, 0, T)]), ("decode_64_rows_ctx_2048", [(i, ctx_len - 1, 1) for i in range(rows)])):
+        ctx = context_for(segs)
+        n = ctx.tokens
+        q = torch.randn(n, Ha * wide, device=device).to(bf)
+        mix = torch.empty(n, Ha * rank, dtype=bf, device=device)
+        ms = timed(lambda: ops.attention_biased(q, plane, plane, ctx.positions, ctx.token_slot, table, page, Ha, 1, wide, rank,
+                                                0.1, mix, window=window, sink=True, sink_logits=sink, ctx=ctx, values_in_keys=True))
+        if what.startswith("prefill"):
+            keys = sum(min(i + 1, window) for i in range(T))
+            kern[f"latent_attention_{what}"] = tensor(2.0 * Ha * (wide + rank) * keys, ms)
+        else:
+            kern[f"latent_attention_{what}"] = hbm(rows * min(window, ctx_len) * wide * 2, ms)
+        q2 = torch.randn(n, Ha * D, device=device).to(bf)
+        o2 = torch.empty_like(q2)
+        ms = timed(lambda: ops.paged_attention(q2, kv_u, ctx.positions, ctx.token_slot, table, page, Ha, G, D, None,
+                                               1.0 / math.sqrt(D), o2, ctx=ctx))
+        if what.startswith("prefill"):
+            kern[f"paged_attention_{what}"] = tensor(4.0 * Ha * D * T * (T + 1) / 2, ms)
+        else:
+            kern[f"paged_attention_{what}"] = hbm(rows * ctx_len * 2 * G * D * 2, ms)
+    ops.check_error_word(device)
+    record["kernels"] = kern
+    clock_record = clocks.stop(windows)
+    first = record["sizes"][sorted(record["sizes"])[0]]["kaketar"]
+    print(json.dumps({"metric": f"decode tok/s @ batch {batch} (Kaketar design sizes, context {context}, 1 B200)",
+                      "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "ms_per_step": first["decode_ms"], "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "design": "kaketar", "clocks": clock_record, "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"]},
+                      **record}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -684,7 +907,7 @@ def main() -> int:
     ap.add_argument("--skip-check", action="store_true", help="leave out the logits check before the timed phases")
     ap.add_argument("--ref-all", action="store_true",
                     help="reference arm: its model_main --bench at batch 1, 8 and 64 instead of --batch alone")
-    ap.add_argument("--design", default=None, choices=["panolorn"],
+    ap.add_argument("--design", default=None, choices=["panolorn", "kaketar"],
                     help="instead of the default workload: this design's prefill and decode throughput at sizes that "
                          "resemble a real model's layers beside Qwen3 dense at equal sizes, and its kernels one by one")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "e2e", "mixed", "p128"],
@@ -694,7 +917,7 @@ def main() -> int:
         if args.gpus != 1 or args.impl != "ours":
             print("bench.py: --design runs this engine on one GPU")
             return 2
-        return design_bench(args)
+        return kaketar_bench(args) if args.design == "kaketar" else design_bench(args)
     if args.model not in MODELS:
         ap.error(f"--model {args.model} goes with --design")
     model_name, model_sizes = MODELS[args.model]

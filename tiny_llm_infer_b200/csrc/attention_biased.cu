@@ -511,7 +511,7 @@ static int launch_biased_prefill(const void* q, const void* kp, const void* vp, 
 }
 
 // ---------------------------------------------------------------- one-token rows, bfloat16, mma.sync
-// One block per (row, key/value head, run of keys).  The query heads of the group are the 16 rows of the
+// One block per (row, key/value head, run of keys) (per sixteen query heads of it, if it serves more).  The query heads of the group are the 16 rows of the
 // tensor-core tile (the first `group` of them real), so keys and values are read once for all of them.
 // The block stages tiles of 64 keys like the prompt kernel; each of its four warps takes 16 keys of a
 // tile and keeps its own running maximum, sum and value sums (base 2), which meet in shared memory in
@@ -525,15 +525,18 @@ attention_biased_decode_kernel(const bf16* q, const bf16* k_plane, const bf16* v
                                const int* __restrict__ rows, const int* __restrict__ block_table, int max_pages,
                                int page_size, int page_shift, int q_heads, int kv_heads, int dk, int dv, ScoreMod mod,
                                const float* __restrict__ slopes, const float* __restrict__ sink_logit, int v_row,
-                               const bf16* gate, int gate_stride, int splits, float* part, bf16* __restrict__ out) {
+                               const bf16* gate, int gate_stride, int splits, int sub_groups, float* part,
+                               bf16* __restrict__ out) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
     TLLM_PDL_ENTER();
     constexpr int kKRow = DKP + kPfPad, kVRow = DVP + kPfPad;
     constexpr int kKBytes = kPfN * kKRow * 2, kVBytes = kPfN * kVRow * 2;
     const int t = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
-    const int g = blockIdx.y, split = blockIdx.z;
-    const int group = q_heads / kv_heads;
-    const int head0 = g * group;
+    // a key/value head's query heads fill the tile's 16 rows; more of them (multi-query attention over many
+    // heads) are dealt to `sub_groups` blocks that read the same keys
+    const int g = blockIdx.y / sub_groups, split = blockIdx.z;
+    const int group = q_heads / kv_heads / sub_groups;
+    const int head0 = g * (q_heads / kv_heads) + (blockIdx.y % sub_groups) * group;
     const int slot = token_slot[t];
     const int rec = dv + 2;
     if (slot < 0) {
@@ -766,6 +769,14 @@ __global__ void attention_biased_combine_kernel(const float* part, const int* __
     }
 }
 
+// Blocks that share a key/value head's query heads in the one-token kernel: the fewest that leave each at
+// most the tile's 16 rows and divide the heads evenly; 0 if there is no such number.
+static int biased_sub_groups(int group) {
+    for (int s = 1; s <= group; ++s)
+        if (group % s == 0 && group / s <= 16) return s;
+    return 0;
+}
+
 template <int DKP, int DVP>
 static int launch_biased_decode(const void* q, const void* kp, const void* vp, long long page_stride,
                                 const int* positions, const int* token_slot, const int* rows, int n_rows,
@@ -780,10 +791,11 @@ static int launch_biased_decode(const void* q, const void* kp, const void* vp, l
         if (e != cudaSuccess) { set_error("attention_biased_decode: %s", cudaGetErrorString(e)); return (int)e; }
         configured.done();
     }
-    launch_pdl(kPdlAttention, attention_biased_decode_kernel<DKP, DVP>, dim3(n_rows, kv_heads, splits), dim3(kPfWarps * 32),
+    const int sub_groups = biased_sub_groups(q_heads / kv_heads);
+    launch_pdl(kPdlAttention, attention_biased_decode_kernel<DKP, DVP>, dim3(n_rows, kv_heads * sub_groups, splits), dim3(kPfWarps * 32),
                smem, stream, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, page_stride, positions, token_slot,
                rows, block_table, max_pages, page_size, page_shift_of(page_size), q_heads, kv_heads, dk, dv, mod, slopes, sink_logit, v_row,
-               (const bf16*)gate, gate_stride, splits, part, (bf16*)out);
+               (const bf16*)gate, gate_stride, splits, sub_groups, part, (bf16*)out);
     if (splits > 1)
         launch_pdl(kPdlCombine, attention_biased_combine_kernel, dim3(n_rows, q_heads), dim3(dv >= 128 ? 128 : 64), 0, stream,
                    (const float*)part, token_slot, rows, q_heads, dv, splits, (const bf16*)gate, gate_stride, (bf16*)out);
@@ -848,7 +860,8 @@ int tllm_attention_biased_general(
 
 // Whether the two bfloat16 kernels below take these sizes (else the general kernel serves).
 int tllm_attention_biased_fast_ok(int q_heads, int kv_heads, int dk, int dv) {
-    return q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16 &&
+    return q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && biased_sub_groups(q_heads / kv_heads) > 0 &&
+           kv_heads * biased_sub_groups(q_heads / kv_heads) <= 65535 &&
            dk % 8 == 0 && dv % 8 == 0 && dk > 0 && dv > 0 && dk <= 128 && dv <= 128;
 }
 
