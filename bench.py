@@ -805,17 +805,18 @@ def kaketar_bench(args) -> int:
     rows = 64
     state = torch.zeros(rows, floats, device=device)
     conv_w = (torch.randn(channels, taps, device=device) * 0.5).to(bf)
+    conv_t = conv_w.t().contiguous()
     dt_bias = torch.randn(Hd * dk, device=device) - 4.0
     rate = torch.ones(Hd, device=device)
     weight = torch.ones(dv, device=device)
     for what, n, seg in (("prefill_2048", T, [[0, 0, T, 0]]), ("decode_64_rows", rows, None)):
-        proj = torch.randn(n, channels + Hd, device=device).to(bf)
+        proj = torch.randn(n, (channels + Hd + 7) // 8 * 8, device=device).to(bf)
         a = torch.randn(n, Hd * dk, device=device)
         gate = torch.randn(n, Hd * dv, device=device)
         slots = torch.zeros(n, dtype=torch.int32, device=device) if seg else torch.arange(n, dtype=torch.int32, device=device)
         seg_info = torch.tensor(seg, dtype=torch.int32, device=device) if seg else None
         ms = timed(lambda: ops.delta_rule(proj, conv_w, taps, a, dt_bias, rate, gate, weight, 1e-6, slots, seg_info, state,
-                                          Hd, Hd, dk, dv, dk ** -0.5, 1e-6, bf))
+                                          Hd, Hd, dk, dv, dk ** -0.5, 1e-6, bf, conv_t=conv_t))
         flops = 6.0 * n * Hd * dk * dv                      # decay and two rank-one steps per element of S, a read-out
         io = n * ((channels + Hd) * 2 + (Hd * dk + Hd * dv) * 4 + Hd * dv * 2) + (0 if seg else 2 * rows * Hd * dk * dv * 4)
         work = n * (2 * Hd * dk + 2 * Hd * dv + Hd * dk + Hd) * 4 * 2      # the float32 hand-over between the three kernels

@@ -12,12 +12,13 @@
 //   delta_scan     one block per (portion, head, group of value columns): a column of S is independent of
 //                  the others, so a thread keeps a slice of one column in registers (the dk rows are dealt
 //                  to R neighbouring lanes, which add their partial dot products with shuffles) and walks
-//                  the portion's tokens, which are staged in shared memory sixteen at a time.
+//                  the portion's tokens, which come through two stages of shared memory sixteen at a time
+//                  (cp.async: the next sixteen are on their way while these are walked).
 //   delta_finish   one block per token: o divided by its root mean square per head, times a weight, times
 //                  sigmoid(gate); the block of a portion's last token also moves the convolution's
 //                  window of the request's state on.
 //
-// State of a request: [heads][per][dv][R] floats of S (row i = il * R + r; rows past dk stay zero), then
+// State of a request: [heads][per][dv][R] floats of S (row i = r * per + il; rows past dk stay zero), then
 // [taps - 1][channels] inputs of the convolution, the newest last.  R and per follow from dk alone
 // (`tllm_delta_rule_lanes`), so every step of a request finds the layout the last one left.
 #include "common.cuh"
@@ -91,6 +92,104 @@ __global__ void delta_prepare_kernel(const T* proj, int ld, const T* __restrict_
     }
 }
 
+// 8-element accesses of either storage type (the convolution's inputs and taps), and of float32
+template <typename T> struct Ld8;
+template <> struct Ld8<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct Ld8<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+// The same with eight channels per thread and access (rows of proj, the taps as [taps][channels], dk and dv
+// multiples of eight, everything on 16-byte boundaries).
+template <typename T>
+__global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restrict__ conv_t, int taps,
+                                         const float* a, int lda, const float* __restrict__ dt_bias,
+                                         const float* __restrict__ rate, const int* __restrict__ token_slot,
+                                         const float* state, long long state_stride, long long tail_off,
+                                         int heads, int kv_heads, int dk, int dv, float q_scale, float unit_eps,
+                                         float* qn, float* kn, float* vv, float* decay, float* beta, int n_rows) {
+    extern __shared__ __align__(16) float y[];   // [2 * kv_heads * dk] q and k after convolution and SiLU
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0) return;
+    const int qk = kv_heads * dk, channels = 2 * qk + heads * dv;
+    int back = 0;
+    for (int j = 1; j < taps; ++j) {
+        if (t - j >= 0 && token_slot[t - j] == slot) back = j;
+        else break;
+    }
+    const float* tail = state + (long long)slot * state_stride + tail_off;
+    for (int c = threadIdx.x * 8; c < channels; c += blockDim.x * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j = 0; j < taps; ++j) {
+            float w[8], x[8];
+            Ld8<T>::load(conv_t + (size_t)(taps - 1 - j) * channels + c, w);
+            if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + c, x);
+            else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+        if (c < 2 * qk) Ld8<float>::store(y + c, acc);
+        else Ld8<float>::store(vv + (size_t)t * heads * dv + (c - 2 * qk), acc);
+    }
+    for (int e = threadIdx.x * 4; e < heads * dk; e += blockDim.x * 4) {
+        const float4 x = *reinterpret_cast<const float4*>(a + (size_t)t * lda + e);
+        const float4 b = *reinterpret_cast<const float4*>(dt_bias + e);
+        const float rt = rate[e / dk];
+        float4 g;
+        g.x = expf(-rt * softplus_f32(x.x + b.x)); g.y = expf(-rt * softplus_f32(x.y + b.y));
+        g.z = expf(-rt * softplus_f32(x.z + b.z)); g.w = expf(-rt * softplus_f32(x.w + b.w));
+        *reinterpret_cast<float4*>(decay + (size_t)t * heads * dk + e) = g;
+    }
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        const float b = to_f32<T>(proj[(size_t)t * ld + channels + h]);
+        beta[(size_t)t * heads + h] = 1.0f / (1.0f + expf(-b));
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int u = warp; u < 2 * kv_heads; u += warps) {          // q heads, then k heads
+        const float* src = y + (size_t)u * dk;
+        float sum = 0.0f;
+        for (int e = lane * 4; e < dk; e += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(src + e);
+            sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        sum = warp_sum(sum);
+        const bool is_q = u < kv_heads;
+        const float sc = (is_q ? q_scale : 1.0f) / sqrtf(sum + unit_eps);
+        float* dst = is_q ? qn + (size_t)t * qk + (size_t)u * dk : kn + (size_t)t * qk + (size_t)(u - kv_heads) * dk;
+        for (int e = lane * 4; e < dk; e += 128) {
+            float4 v = *reinterpret_cast<const float4*>(src + e);
+            v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+            *reinterpret_cast<float4*>(dst + e) = v;
+        }
+    }
+}
+
 // ---------------------------------------------------------------- scan
 template <int R>
 __device__ __forceinline__ float lanes_sum(float v) {
@@ -99,12 +198,38 @@ __device__ __forceinline__ float lanes_sum(float v) {
     return v;
 }
 
-template <int R>
-__global__ void delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ token_slot,
-                                  const float* qn, const float* kn, const float* vv, const float* decay,
-                                  const float* beta, float* state, long long state_stride, int heads,
-                                  int kv_heads, int dk, int dv, int cols, float* o_raw) {
-    extern __shared__ float sm[];
+__device__ __forceinline__ void cp_async_f32(float* dst, const float* src, bool valid) {
+    const int bytes = valid ? 4 : 0;                 // zero fill where there is nothing to read
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+// A lane r of a column keeps the rows i = r * per + il, il < per, as PER registers; in shared memory a token's
+// k (and q, g) row is laid out [R][PER + 4]: a lane's rows are neighbours, so it reads them four at a time, and
+// the four floats between the lanes' runs keep those reads off each other's banks.
+template <int R, int PER>
+struct ScanLayout {
+    static constexpr int kRow = R * (PER + 4);                               // floats of one token's k (or q, g) row
+    __host__ __device__ static constexpr int stage_floats(int cols) {       // k, q, g, the value columns, the betas
+        return (kScanChunk * (3 * kRow + cols + 1) + 3) / 4 * 4;
+    }
+};
+
+// R lanes share a column, each keeps PER rows of it at most.  The chunks of tokens come through two stages
+// filled by cp.async, so that the next chunk is on its way while this one is walked.  A token's step, per
+// thread: S <- g S, dot = sum S k, u = beta (v - dot), S <- S + k u, o = sum S q.  Only S is carried from token
+// to token; the read-out's sum is off that path.
+template <int R, int PER>
+__global__ void __launch_bounds__(256, 2)
+delta_scan_kernel(const int* __restrict__ seg_info, const int* __restrict__ token_slot,
+                  const float* qn, const float* kn, const float* vv, const float* decay,
+                  const float* beta, float* state, long long state_stride, int heads,
+                  int kv_heads, int dk, int dv, int cols, int vec, float* o_raw) {
+    extern __shared__ __align__(16) float sm[];
+    using L = ScanLayout<R, PER>;
+    constexpr int kLane = PER + 4;
     TLLM_PDL_ENTER();
     const int seg = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
     int slot, start, len;
@@ -114,66 +239,130 @@ __global__ void delta_scan_kernel(const int* __restrict__ seg_info, const int* _
         slot = token_slot[seg]; start = seg; len = 1;
     }
     if (slot < 0 || len <= 0) return;
-    const int per = (dk + R - 1) / R, dkp = per * R;
+    const int per = (dk + R - 1) / R;
     const int r = threadIdx.x % R, jl = threadIdx.x / R;       // lane of the column, column of the block
     const int j = col0 + jl;
-    const bool live = jl < cols && j < dv;
+    const bool live = j < dv;
     const int kvh = head / (heads / kv_heads);
-    float* k_s = sm;                                  // [chunk][dkp]
-    float* q_s = k_s + kScanChunk * dkp;              // [chunk][dkp]
-    float* g_s = q_s + kScanChunk * dkp;              // [chunk][dkp]
-    float* v_s = g_s + kScanChunk * dkp;              // [chunk][cols]
-    float* o_s = v_s + kScanChunk * cols;             // [chunk][cols]
-    float* b_s = o_s + kScanChunk * cols;             // [chunk]
+    const int stage_floats = L::stage_floats(cols);
+    float* o_s = sm + 2 * stage_floats;               // [chunk][cols]
+    // rows that no copy writes (past per in a lane, past dk in the last lanes) are zeros: they add nothing
+    if (per < PER || dk < R * per) {
+        for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) sm[i] = 0.0f;
+        __syncthreads();
+    }
 
-    float* st = state + (long long)slot * state_stride + (size_t)head * per * dv * R;
-    float S[kScanMaxPer];
-#pragma unroll
-    for (int il = 0; il < kScanMaxPer; ++il)
-        S[il] = (live && il < per) ? st[((size_t)il * dv + j) * R + r] : 0.0f;
-
-    for (int c0 = 0; c0 < len; c0 += kScanChunk) {
+    auto issue = [&](int c0, int st) {
         const int n = min(kScanChunk, len - c0);
-        __syncthreads();                              // the chunk before has been written out
-        for (int i = threadIdx.x; i < n * dkp; i += blockDim.x) {
-            const int tt = i / dkp, e = i - tt * dkp;
-            const size_t row = (size_t)(start + c0 + tt);
-            const bool in = e < dk;
-            k_s[i] = in ? kn[(row * kv_heads + kvh) * dk + e] : 0.0f;
-            q_s[i] = in ? qn[(row * kv_heads + kvh) * dk + e] : 0.0f;
-            g_s[i] = in ? decay[(row * heads + head) * dk + e] : 0.0f;
+        float* k_s = sm + st * stage_floats;
+        float* q_s = k_s + kScanChunk * L::kRow;
+        float* g_s = q_s + kScanChunk * L::kRow;
+        float* v_s = g_s + kScanChunk * L::kRow;
+        float* b_s = v_s + kScanChunk * cols;
+        if (vec) {                                    // dk and per multiples of four: four rows of one lane at a time
+            const int quads = dk >> 2;
+            for (int i = threadIdx.x; i < n * quads; i += blockDim.x) {
+                const int tt = i / quads, e = (i - tt * quads) * 4;
+                const int at = tt * L::kRow + (e / per) * kLane + e % per;
+                const size_t row = (size_t)(start + c0 + tt);
+                cp_async_f32x4(k_s + at, kn + (row * kv_heads + kvh) * dk + e);
+                cp_async_f32x4(q_s + at, qn + (row * kv_heads + kvh) * dk + e);
+                cp_async_f32x4(g_s + at, decay + (row * heads + head) * dk + e);
+            }
+        } else {
+            for (int i = threadIdx.x; i < n * dk; i += blockDim.x) {
+                const int tt = i / dk, e = i - tt * dk;
+                const int at = tt * L::kRow + (e / per) * kLane + e % per;
+                const size_t row = (size_t)(start + c0 + tt);
+                cp_async_f32(k_s + at, kn + (row * kv_heads + kvh) * dk + e, true);
+                cp_async_f32(q_s + at, qn + (row * kv_heads + kvh) * dk + e, true);
+                cp_async_f32(g_s + at, decay + (row * heads + head) * dk + e, true);
+            }
         }
         for (int i = threadIdx.x; i < n * cols; i += blockDim.x) {
             const int tt = i / cols, e = i - tt * cols;
-            v_s[i] = (col0 + e < dv) ? vv[((size_t)(start + c0 + tt) * heads + head) * dv + col0 + e] : 0.0f;
+            const bool in = col0 + e < dv;
+            cp_async_f32(v_s + i, vv + ((size_t)(start + c0 + tt) * heads + head) * dv + (in ? col0 + e : 0), in);
         }
-        for (int i = threadIdx.x; i < n; i += blockDim.x) b_s[i] = beta[(size_t)(start + c0 + i) * heads + head];
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            cp_async_f32(b_s + i, beta + (size_t)(start + c0 + i) * heads + head, true);
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    issue(0, 0);
+    // in the request's state the element (row r * per + il, column j) lies at [il][j][r]: a warp reads whole lines
+    float* st_ptr = state + (long long)slot * state_stride + (size_t)head * per * dv * R;
+    float2 S2[PER / 2];                               // rows il = 2 p and 2 p + 1 of this lane
+#pragma unroll
+    for (int il = 0; il < PER; il += 2) {
+        S2[il >> 1].x = (live && il < per) ? st_ptr[((size_t)il * dv + j) * R + r] : 0.0f;
+        S2[il >> 1].y = (live && il + 1 < per) ? st_ptr[((size_t)(il + 1) * dv + j) * R + r] : 0.0f;
+    }
+
+    int stage = 0;
+    for (int c0 = 0; c0 < len; c0 += kScanChunk, stage ^= 1) {
+        const int n = min(kScanChunk, len - c0);
+        if (c0 + kScanChunk < len) {
+            issue(c0 + kScanChunk, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
-        {   // every thread walks the tokens (the shuffles want whole warps); one without a column carries zeros
+        const float* k_s = sm + stage * stage_floats;
+        const float* q_s = k_s + kScanChunk * L::kRow;
+        const float* g_s = q_s + kScanChunk * L::kRow;
+        const float* v_s = g_s + kScanChunk * L::kRow;
+        const float* b_s = v_s + kScanChunk * cols;
+        // every thread walks the tokens (the shuffles want whole warps); one without a column carries zeros
+        // two rows at a time with the packed float32 instructions of sm_100 (each half rounds as the scalar
+        // instruction would): Sg = S g, dot += Sg k, S = Sg + k u, o += S q: four instructions for two rows
+        auto step = [&](int tt) -> float {
+            const float4* kr = reinterpret_cast<const float4*>(k_s + tt * L::kRow + r * kLane);
+            const float4* qr = reinterpret_cast<const float4*>(q_s + tt * L::kRow + r * kLane);
+            const float4* gr = reinterpret_cast<const float4*>(g_s + tt * L::kRow + r * kLane);
+            float2 kk[PER / 2];
+            float2 dot_a = make_float2(0.0f, 0.0f), dot_b = dot_a;
+#pragma unroll
+            for (int il = 0; il < PER; il += 4) {
+                const float4 k4 = kr[il >> 2], g4 = gr[il >> 2];
+                kk[il >> 1] = make_float2(k4.x, k4.y);
+                kk[(il >> 1) + 1] = make_float2(k4.z, k4.w);
+                S2[il >> 1] = __fmul2_rn(S2[il >> 1], make_float2(g4.x, g4.y));
+                S2[(il >> 1) + 1] = __fmul2_rn(S2[(il >> 1) + 1], make_float2(g4.z, g4.w));
+                dot_a = __ffma2_rn(S2[il >> 1], kk[il >> 1], dot_a);
+                dot_b = __ffma2_rn(S2[(il >> 1) + 1], kk[(il >> 1) + 1], dot_b);
+            }
+            const float2 dsum = __fadd2_rn(dot_a, dot_b);
+            const float dot = lanes_sum<R>(dsum.x + dsum.y);
+            const float u = b_s[tt] * (v_s[tt * cols + jl] - dot);
+            const float2 u2 = make_float2(u, u);
+            float2 o_a = make_float2(0.0f, 0.0f), o_b = o_a;
+#pragma unroll
+            for (int il = 0; il < PER; il += 4) {
+                const float4 q4 = qr[il >> 2];
+                S2[il >> 1] = __ffma2_rn(kk[il >> 1], u2, S2[il >> 1]);
+                S2[(il >> 1) + 1] = __ffma2_rn(kk[(il >> 1) + 1], u2, S2[(il >> 1) + 1]);
+                o_a = __ffma2_rn(S2[il >> 1], make_float2(q4.x, q4.y), o_a);
+                o_b = __ffma2_rn(S2[(il >> 1) + 1], make_float2(q4.z, q4.w), o_b);
+            }
+            const float2 osum = __fadd2_rn(o_a, o_b);
+            return lanes_sum<R>(osum.x + osum.y);
+        };
+        if (n == kScanChunk) {
+            // a whole chunk: unrolled, the read-outs kept in registers until the end, so that no store to shared
+            // memory stands between a token's loads and the next one's and they can be issued ahead
+            float o_reg[kScanChunk];
+#pragma unroll
+            for (int tt = 0; tt < kScanChunk; ++tt) o_reg[tt] = step(tt);
+            if (r == 0) {
+#pragma unroll
+                for (int tt = 0; tt < kScanChunk; ++tt) o_s[tt * cols + jl] = o_reg[tt];
+            }
+        } else {
             for (int tt = 0; tt < n; ++tt) {
-                const float* kr = k_s + tt * dkp + r;
-                const float* qr = q_s + tt * dkp + r;
-                const float* gr = g_s + tt * dkp + r;
-                float kk[kScanMaxPer];
-                float dot = 0.0f;
-#pragma unroll
-                for (int il = 0; il < kScanMaxPer; ++il)
-                    if (il < per) {
-                        kk[il] = kr[il * R];
-                        S[il] *= gr[il * R];
-                        dot += S[il] * kk[il];
-                    }
-                dot = lanes_sum<R>(dot);
-                const float u = b_s[tt] * (v_s[tt * cols + jl] - dot);
-                float oq = 0.0f;
-#pragma unroll
-                for (int il = 0; il < kScanMaxPer; ++il)
-                    if (il < per) {
-                        S[il] += kk[il] * u;
-                        oq += S[il] * qr[il * R];
-                    }
-                oq = lanes_sum<R>(oq);
-                if (r == 0 && live) o_s[tt * cols + jl] = oq;
+                const float oq = step(tt);
+                if (r == 0) o_s[tt * cols + jl] = oq;
             }
         }
         __syncthreads();
@@ -184,8 +373,10 @@ __global__ void delta_scan_kernel(const int* __restrict__ seg_info, const int* _
     }
     if (live) {
 #pragma unroll
-        for (int il = 0; il < kScanMaxPer; ++il)
-            if (il < per) st[((size_t)il * dv + j) * R + r] = S[il];
+        for (int il = 0; il < PER; il += 2) {
+            if (il < per) st_ptr[((size_t)il * dv + j) * R + r] = S2[il >> 1].x;
+            if (il + 1 < per) st_ptr[((size_t)(il + 1) * dv + j) * R + r] = S2[il >> 1].y;
+        }
     }
 }
 
@@ -232,6 +423,58 @@ __global__ void delta_finish_kernel(const float* o_raw, const float* gate, int l
     }
 }
 
+// The same with four elements per lane and access, and the window of the convolution moved eight channels at a
+// time (dv a multiple of four, channels and the rows of proj multiples of eight, 16-byte boundaries).
+template <typename T>
+__global__ void delta_finish_vec_kernel(const float* o_raw, const float* gate, int ldg, const float* __restrict__ weight,
+                                        float eps, const int* __restrict__ token_slot, int n_rows, int heads, int dv,
+                                        T* out, const T* proj, int ld, int channels, int taps, float* state,
+                                        long long state_stride, long long tail_off) {
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    const int slot = token_slot[t];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    if (slot < 0) {
+        for (int e = threadIdx.x; e < heads * dv; e += blockDim.x) out[(size_t)t * heads * dv + e] = from_f32<T>(0.0f);
+        return;
+    }
+    for (int h = warp; h < heads; h += warps) {
+        const float* src = o_raw + ((size_t)t * heads + h) * dv;
+        float sum = 0.0f;
+        for (int e = lane * 4; e < dv; e += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(src + e);
+            sum += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        sum = warp_sum(sum);
+        const float sc = 1.0f / sqrtf(sum / (float)dv + eps);
+        for (int e = lane * 4; e < dv; e += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(src + e);
+            const float4 g = *reinterpret_cast<const float4*>(gate + (size_t)t * ldg + (size_t)h * dv + e);
+            const float4 w = *reinterpret_cast<const float4*>(weight + e);
+            T* dst = out + ((size_t)t * heads + h) * dv + e;
+            dst[0] = from_f32<T>(v.x * sc * w.x / (1.0f + expf(-g.x)));
+            dst[1] = from_f32<T>(v.y * sc * w.y / (1.0f + expf(-g.y)));
+            dst[2] = from_f32<T>(v.z * sc * w.z / (1.0f + expf(-g.z)));
+            dst[3] = from_f32<T>(v.w * sc * w.w / (1.0f + expf(-g.w)));
+        }
+    }
+    if (taps > 1 && (t + 1 >= n_rows || token_slot[t + 1] != slot)) {
+        int len = 1;
+        while (len < taps - 1 && t - len >= 0 && token_slot[t - len] == slot) ++len;
+        float* tail = state + (long long)slot * state_stride + tail_off;
+        const int keep = taps - 1;
+        for (int c = threadIdx.x * 8; c < channels; c += blockDim.x * 8) {
+            for (int i = 0; i < keep; ++i) {         // ascending: an old entry is read before its place is written
+                const int from_end = keep - i;
+                float x[8];
+                if (from_end <= len) Ld8<T>::load(proj + (size_t)(t + 1 - from_end) * ld + c, x);
+                else Ld8<float>::load(tail + (size_t)(i + len) * channels + c, x);
+                Ld8<float>::store(tail + (size_t)i * channels + c, x);
+            }
+        }
+    }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
@@ -247,8 +490,9 @@ long long tllm_delta_rule_state_floats(int heads, int kv_heads, int dk, int dv, 
     return (long long)heads * per * r * dv + (long long)(taps - 1) * (2 * kv_heads * dk + heads * dv);
 }
 
-int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, int taps, const float* a, int lda,
-                       const float* dt_bias, const float* rate, const int* token_slot, const float* state,
+// conv_w [channels, taps], and conv_t, the same taps as [taps, channels] (null: the scalar kernel serves).
+int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, const void* conv_t, int taps, const float* a,
+                       int lda, const float* dt_bias, const float* rate, const int* token_slot, const float* state,
                        long long state_stride, int heads, int kv_heads, int dk, int dv, float q_scale,
                        float unit_eps, float* qn, float* kn, float* vv, float* decay, float* beta, int n_rows,
                        cudaStream_t stream) {
@@ -256,14 +500,28 @@ int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, 
                  "delta_prepare: bad sizes");
     const int channels = 2 * kv_heads * dk + heads * dv;
     TLLM_REQUIRE(ld >= channels + heads && lda >= heads * dk, "delta_prepare: rows too short");
-    const size_t smem = (size_t)channels * sizeof(float);
-    TLLM_REQUIRE(smem <= 200 * 1024, "delta_prepare: %d channels do not fit in shared memory", channels);
     if (n_rows == 0) return 0;
     const int r = delta_lanes(dk), per = (dk + r - 1) / r;
     TLLM_REQUIRE(per <= kScanMaxPer, "delta_prepare: keys of width %d are too wide", dk);
     const long long tail_off = (long long)heads * per * r * dv;
+    const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = conv_t != nullptr && dk % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && lda % 4 == 0 && tail_off % 4 == 0 &&
+                     state_stride % 4 == 0 && al(proj) && al(conv_t) && al(a) && al(dt_bias) && al(state) && al(qn) && al(kn) &&
+                     al(vv) && al(decay);
+    const size_t smem = (size_t)(vec ? 2 * kv_heads * dk : channels) * sizeof(float);
+    TLLM_REQUIRE(smem <= 200 * 1024, "delta_prepare: %d channels do not fit in shared memory", channels);
 #define PREP(T)                                                                                                  \
     do {                                                                                                         \
+        if (vec) {                                                                                               \
+            if (smem > 48 * 1024) {                                                                              \
+                cudaError_t e = cudaFuncSetAttribute(delta_prepare_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+                if (e != cudaSuccess) { set_error("delta_prepare: %s", cudaGetErrorString(e)); return (int)e; }  \
+            }                                                                                                    \
+            launch_pdl(kPdlOther, delta_prepare_vec_kernel<T>, dim3(n_rows), dim3(256), smem, stream, (const T*)proj, ld, \
+                       (const T*)conv_t, taps, a, lda, dt_bias, rate, token_slot, state, state_stride, tail_off, \
+                       heads, kv_heads, dk, dv, q_scale, unit_eps, qn, kn, vv, decay, beta, n_rows);             \
+            break;                                                                                               \
+        }                                                                                                        \
         if (smem > 48 * 1024) {                                                                                  \
             cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) { set_error("delta_prepare: %s", cudaGetErrorString(e)); return (int)e; }      \
@@ -289,31 +547,39 @@ int tllm_delta_scan(const int* seg_info, int segments, const int* token_slot, co
     if (segments == 0) return 0;
     const int r = delta_lanes(dk), per = (dk + r - 1) / r;
     TLLM_REQUIRE(per <= kScanMaxPer, "delta_scan: keys of width %d are too wide", dk);
-    // columns per block: whole warps, at most 256 threads, and at least two blocks per multiprocessor in all
-    // where the value width allows it
+    // columns per block: whole warps, at most 256 threads, not wider than the values, and at least a block per
+    // multiprocessor in all where the value width allows it (a column does not depend on the others, so the
+    // result is the same however they are dealt)
     int cols = 256 / r;
     const int min_cols = 32 / r > 1 ? 32 / r : 1;
     const int sms = sm_count_cached() > 0 ? sm_count_cached() : 148;
     while (cols > min_cols && cols / 2 >= dv) cols /= 2;
-    while (cols > min_cols && (long long)segments * heads * ((dv + cols - 1) / cols) < 2LL * sms) cols /= 2;
+    while (cols > min_cols && (long long)segments * heads * ((dv + cols - 1) / cols) < sms) cols /= 2;
     const int col_blocks = (dv + cols - 1) / cols;
     const int threads = cols * r;
-    const size_t smem = (size_t)kScanChunk * (3 * per * r + 2 * cols + 1) * sizeof(float);
-    TLLM_REQUIRE(smem <= 200 * 1024 && col_blocks <= 65535, "delta_scan: sizes %d x %d do not fit", dk, dv);
-#define SCAN(RR)                                                                                                 \
+    TLLM_REQUIRE(col_blocks <= 65535, "delta_scan: sizes %d x %d do not fit", dk, dv);
+    const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const int vec = dk % 4 == 0 && per % 4 == 0 && aligned(qn) && aligned(kn) && aligned(decay);
+#define SCAN(RR, PP)                                                                                             \
     do {                                                                                                         \
-        if (smem > 48 * 1024) {                                                                                  \
-            cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        const size_t smem = ((size_t)2 * ScanLayout<RR, PP>::stage_floats(cols) + (size_t)kScanChunk * cols) * sizeof(float); \
+        TLLM_REQUIRE(smem <= 200 * 1024, "delta_scan: sizes %d x %d do not fit", dk, dv);                         \
+        static OncePerDevice configured;                                                                         \
+        if (configured.first()) {                                                                                \
+            cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<RR, PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (e != cudaSuccess) { set_error("delta_scan: %s", cudaGetErrorString(e)); return (int)e; }         \
+            configured.done();                                                                                   \
         }                                                                                                        \
-        launch_pdl(kPdlOther, delta_scan_kernel<RR>, dim3(segments, heads, col_blocks), dim3(threads), smem, stream, \
+        launch_pdl(kPdlOther, delta_scan_kernel<RR, PP>, dim3(segments, heads, col_blocks), dim3(threads), smem, stream, \
                    seg_info, token_slot, qn, kn, vv, decay, beta, state, state_stride, heads, kv_heads, dk, dv,  \
-                   cols, o_raw);                                                                                 \
+                   cols, vec, o_raw);                                                                            \
     } while (0)
-    if (r == 4) SCAN(4);
-    else if (r == 8) SCAN(8);
-    else if (r == 16) SCAN(16);
-    else SCAN(32);
+    if (r == 4 && per <= 4) SCAN(4, 4);
+    else if (r == 4 && per <= 8) SCAN(4, 8);
+    else if (r == 4) SCAN(4, 16);
+    else if (r == 8) SCAN(8, 16);
+    else if (r == 16) SCAN(16, 16);
+    else SCAN(32, 16);
 #undef SCAN
     return finish_launch("delta_scan");
 }
@@ -327,13 +593,22 @@ int tllm_delta_finish(const float* o_raw, const float* gate, int ldg, const floa
     const int channels = 2 * kv_heads * dk + heads * dv;
     const int r = delta_lanes(dk), per = (dk + r - 1) / r;
     const long long tail_off = (long long)heads * per * r * dv;
-    if (dtype == kBF16)
-        launch_pdl(kPdlOther, delta_finish_kernel<bf16>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps,
-                   token_slot, n_rows, heads, dv, (bf16*)out, (const bf16*)proj, ld, channels, taps, state, state_stride, tail_off);
-    else if (dtype == kF32)
-        launch_pdl(kPdlOther, delta_finish_kernel<float>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps,
-                   token_slot, n_rows, heads, dv, (float*)out, (const float*)proj, ld, channels, taps, state, state_stride, tail_off);
+    const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool vec = dv % 4 == 0 && ldg % 4 == 0 && channels % 8 == 0 && ld % 8 == 0 && tail_off % 4 == 0 && state_stride % 4 == 0 &&
+                     al(o_raw) && al(gate) && al(weight) && al(proj) && al(state);
+#define FIN(T)                                                                                                             \
+    do {                                                                                                                   \
+        if (vec)                                                                                                           \
+            launch_pdl(kPdlOther, delta_finish_vec_kernel<T>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps, \
+                       token_slot, n_rows, heads, dv, (T*)out, (const T*)proj, ld, channels, taps, state, state_stride, tail_off); \
+        else                                                                                                               \
+            launch_pdl(kPdlOther, delta_finish_kernel<T>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps, \
+                       token_slot, n_rows, heads, dv, (T*)out, (const T*)proj, ld, channels, taps, state, state_stride, tail_off); \
+    } while (0)
+    if (dtype == kBF16) FIN(bf16);
+    else if (dtype == kF32) FIN(float);
     else TLLM_REQUIRE(false, "delta_finish: unknown dtype %d", dtype);
+#undef FIN
     return finish_launch("delta_finish");
 }
 

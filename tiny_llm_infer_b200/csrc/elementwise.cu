@@ -383,6 +383,68 @@ __global__ void embedding_norm_kernel(const int* __restrict__ ids, const int* __
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = dst[i] * sc * gain[i];
 }
 
+// Vector form: the row stays in registers between the sum and the scaling (hidden a multiple of 8, at most
+// blockDim * 8 * CHUNKS).
+template <typename TW, int CHUNKS>
+__global__ void embedding_norm_vec_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                          const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                                          const float* __restrict__ gain, float eps, float scale, float* __restrict__ out,
+                                          int hidden, int vocab, int max_positions) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    float* dst = out + (size_t)t * hidden;
+    const int n_chunks = hidden >> 3;
+    if (id < 0) {
+        const float zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) Vec8<float>::store(dst + c * 8, zero);
+        return;
+    }
+    if (id >= vocab) id = vocab - 1;
+    const TW* src = table + (size_t)id * hidden;
+    const TW* prow = nullptr;
+    if (pos_table != nullptr) {
+        int p = positions[t];
+        p = p < 0 ? 0 : (p >= max_positions ? max_positions - 1 : p);
+        prow = pos_table + (size_t)p * hidden;
+    }
+    float v[CHUNKS][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<TW>::load(src + c * 8, v[j]);
+            float p[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (prow != nullptr) Vec8<TW>::load(prow + c * 8, p);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[j][e] = v[j][e] * scale + p[e];
+                sum += v[j][e] * v[j][e];
+            }
+        }
+    }
+    float sc = 1.0f;
+    if (gain != nullptr) {
+        sum = block_sum(sum, scratch);
+        sc = 1.0f / sqrtf(sum / (float)hidden + eps);
+    }
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            if (gain != nullptr) {
+                float g[8];
+                Vec8<float>::load(gain + c * 8, g);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j][e] = v[j][e] * sc * g[e];
+            }
+            Vec8<float>::store(dst + c * 8, v[j]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- residual sum without a norm behind it
 // For blocks whose sub-layers read the stream itself: h[r, :] += d' and out[r, :] = h[r, :] in the storage
 // type, with d' = delta, or, with `post_gain`, post_gain * delta / sqrt(mean(delta^2) + post_eps) in float32.
@@ -415,6 +477,58 @@ __global__ void stream_add_kernel(float* h, const TD* delta, const TG* __restric
     }
 }
 
+// Vector form of stream_add: the row lives in registers between the delta's sum of squares and the writes
+// (width a multiple of 8, at most blockDim * 8 * CHUNKS).
+template <typename TD, typename TG, typename TO, int CHUNKS>
+__global__ void stream_add_vec_kernel(float* h, const TD* delta, const TG* __restrict__ post_gain, float post_eps,
+                                      TO* __restrict__ out, int width) {
+    __shared__ float scratch[32];
+    TLLM_PDL_ENTER();
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * width;
+    TO* dst = out + (size_t)r * width;
+    const TD* dr = delta != nullptr ? delta + (size_t)r * width : nullptr;
+    const int n_chunks = width >> 3;
+    float v[CHUNKS][8], d[CHUNKS][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            Vec8<float>::load(hr + c * 8, v[j]);
+            if (dr != nullptr) {
+                Vec8<TD>::load(dr + c * 8, d[j]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum += d[j][e] * d[j][e];
+            }
+        }
+    }
+    float post_scale = 1.0f;
+    if (post_gain != nullptr) {
+        sum = block_sum(sum, scratch);
+        post_scale = 1.0f / sqrtf(sum / (float)width + post_eps);
+    }
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < n_chunks) {
+            if (dr != nullptr) {
+                if (post_gain != nullptr) {
+                    float g[8];
+                    Vec8<TG>::load(post_gain + c * 8, g);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j][e] += d[j][e] * post_scale * g[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j][e] += d[j][e];
+                }
+                Vec8<float>::store(hr + c * 8, v[j]);
+            }
+            Vec8<TO>::store(dst + c * 8, v[j]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- activations
 // out = act(x) (codes of `gate_act`), or, with a table, out[t, j] = act(x[t, j]) * table[ids[t], col0 + j]:
 // a gate on a per-token vector looked up by the token's id.
@@ -434,6 +548,21 @@ __global__ void activation_kernel(const T* x, T* out, int act, int width, size_t
             v *= to_f32<T>(table[(size_t)id * ldt + col0 + j]);
         }
         out[idx] = from_f32<T>(v);
+    }
+}
+
+// Vector form without a table: eight elements per access.
+template <typename T>
+__global__ void activation_vec_kernel(const T* x, T* out, int act, size_t chunks) {
+    TLLM_PDL_ENTER();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < chunks; idx += stride) {
+        float v[8];
+        Vec8<T>::load(x + idx * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = gate_act(v[e], act);
+        Vec8<T>::store(out + idx * 8, v);
     }
 }
 
@@ -558,6 +687,18 @@ int tllm_embedding_norm(const int* ids, const int* positions, const void* table,
     TLLM_REQUIRE(gain == nullptr || eps > 0.0f, "embedding_norm: eps must be positive");
     if (tokens == 0) return 0;
     const int block = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (hidden % 8 == 0 && hidden / 8 <= 1024 * 4 && aligned16(table) && aligned16(pos_table) && aligned16(gain) && aligned16(out)
+        && (table_dtype == kBF16 || table_dtype == kF32)) {
+        int vblock = 64;
+        while (vblock < 1024 && vblock < hidden / 8) vblock *= 2;
+        const int per_thread = (hidden / 8 + vblock - 1) / vblock;
+#define EVEC(TW, C) launch_pdl(kPdlOther, embedding_norm_vec_kernel<TW, C>, dim3(tokens), dim3(vblock), 0, stream, ids, positions, \
+                               (const TW*)table, (const TW*)pos_table, gain, eps, scale, out, hidden, vocab, max_positions)
+        if (table_dtype == kBF16) { if (per_thread <= 1) EVEC(bf16, 1); else if (per_thread <= 2) EVEC(bf16, 2); else EVEC(bf16, 4); }
+        else { if (per_thread <= 1) EVEC(float, 1); else if (per_thread <= 2) EVEC(float, 2); else EVEC(float, 4); }
+#undef EVEC
+        return finish_launch("embedding_norm");
+    }
     if (table_dtype == kBF16)
         launch_pdl(kPdlOther, embedding_norm_kernel<bf16>, dim3(tokens), dim3(block), 0, stream, ids, positions, (const bf16*)table,
                    (const bf16*)pos_table, gain, eps, scale, out, hidden, vocab, max_positions);
@@ -576,8 +717,25 @@ int tllm_stream_add(float* h, const void* delta, const void* post_gain, int gain
     TLLM_REQUIRE(gain_dtype == kBF16 || gain_dtype == kF32, "stream_add: unknown gain dtype");
     if (rows == 0) return 0;
     const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-#define SADD(TD, TG, TO) launch_pdl(kPdlNorm, stream_add_kernel<TD, TG, TO>, dim3(rows), dim3(block), 0, stream, h, (const TD*)delta, \
-                                    (const TG*)post_gain, post_eps, (TO*)out, width)
+    const bool vec = width % 8 == 0 && aligned16(h) && aligned16(delta) && aligned16(post_gain) && aligned16(out) && width / 8 <= 1024 * 4;
+    int vblock = 64;
+    while (vblock < 1024 && vblock < width / 8) vblock *= 2;
+    const int per_thread = vec ? (width / 8 + vblock - 1) / vblock : 0;
+#define SADD(TD, TG, TO)                                                                                                   \
+    do {                                                                                                                   \
+        if (vec && per_thread <= 1)                                                                                        \
+            launch_pdl(kPdlNorm, stream_add_vec_kernel<TD, TG, TO, 1>, dim3(rows), dim3(vblock), 0, stream, h, (const TD*)delta, \
+                       (const TG*)post_gain, post_eps, (TO*)out, width);                                                   \
+        else if (vec && per_thread <= 2)                                                                                   \
+            launch_pdl(kPdlNorm, stream_add_vec_kernel<TD, TG, TO, 2>, dim3(rows), dim3(vblock), 0, stream, h, (const TD*)delta, \
+                       (const TG*)post_gain, post_eps, (TO*)out, width);                                                   \
+        else if (vec)                                                                                                      \
+            launch_pdl(kPdlNorm, stream_add_vec_kernel<TD, TG, TO, 4>, dim3(rows), dim3(vblock), 0, stream, h, (const TD*)delta, \
+                       (const TG*)post_gain, post_eps, (TO*)out, width);                                                   \
+        else                                                                                                               \
+            launch_pdl(kPdlNorm, stream_add_kernel<TD, TG, TO>, dim3(rows), dim3(block), 0, stream, h, (const TD*)delta,   \
+                       (const TG*)post_gain, post_eps, (TO*)out, width);                                                   \
+    } while (0)
     if (act_dtype == kBF16) { if (gain_dtype == kBF16) SADD(bf16, bf16, bf16); else SADD(bf16, float, bf16); }
     else if (act_dtype == kF32) { if (gain_dtype == kBF16) SADD(float, bf16, float); else SADD(float, float, float); }
     else TLLM_REQUIRE(false, "stream_add: unknown dtype %d", act_dtype);
@@ -601,6 +759,15 @@ int tllm_activation(const void* x, void* out, int dtype, int act, int tokens, in
     const size_t total = (size_t)tokens * width;
     if (total == 0) return 0;
     const int block = 256, grid = grid_for(total, block);
+    if (table == nullptr && total % 8 == 0 && aligned16(x) && aligned16(out) && (dtype == kBF16 || dtype == kF32)) {
+        const size_t chunks = total / 8;
+        const int vgrid = grid_for(chunks, block);
+        if (dtype == kBF16)
+            launch_pdl(kPdlSwiglu, activation_vec_kernel<bf16>, dim3(vgrid), dim3(block), 0, stream, (const bf16*)x, (bf16*)out, act, chunks);
+        else
+            launch_pdl(kPdlSwiglu, activation_vec_kernel<float>, dim3(vgrid), dim3(block), 0, stream, (const float*)x, (float*)out, act, chunks);
+        return finish_launch("activation");
+    }
     if (dtype == kBF16)
         launch_pdl(kPdlSwiglu, activation_kernel<bf16>, dim3(grid), dim3(block), 0, stream, (const bf16*)x, (bf16*)out, act, width, total,
                    ids, (const bf16*)table, ldt, col0, vocab);

@@ -75,7 +75,7 @@ def _declare(h) -> None:
         "tllm_softcap": [vp, f32, i64, vp],
         "tllm_stream_add": [vp, vp, vp, i32, f32, vp, i32, i32, i32, vp],
         "tllm_activation": [vp, vp, i32, i32, i32, i32, vp, vp, i32, i32, i32, vp],
-        "tllm_delta_prepare": [vp, i32, i32, vp, i32, vp, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, f32,
+        "tllm_delta_prepare": [vp, i32, i32, vp, vp, i32, vp, i32, vp, vp, vp, vp, i64, i32, i32, i32, i32, f32, f32,
                                vp, vp, vp, vp, vp, i32, vp],
         "tllm_delta_scan": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
         "tllm_delta_finish": [vp, vp, i32, vp, f32, vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64, vp],
@@ -780,15 +780,16 @@ def delta_rule_state_floats(heads: int, kv_heads: int, dk: int, dv: int, taps: i
 def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, a: torch.Tensor, dt_bias: torch.Tensor,
                rate: torch.Tensor, gate: torch.Tensor, out_weight: torch.Tensor, eps: float, token_slot: torch.Tensor,
                seg_info: Optional[torch.Tensor], state: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
-               q_scale: float, unit_eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+               q_scale: float, unit_eps: float, out_dtype: torch.dtype, conv_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One step of the delta rule with a decay per head and key channel for every row of ``proj`` [T, >= channels
     + heads] = q channels | k channels | v channels | beta logits (storage type): convolution with ``conv_w``
     [channels, taps] and SiLU, unit q and k, g = exp(-rate_h softplus(a + dt_bias)) with ``a`` [T, heads * dk]
     float32, the recurrence over each portion's rows from ``state[slot]`` (float32, updated in place), then the
     read-out divided by its root mean square per head, times ``out_weight`` [dv] float32, times sigmoid(``gate``)
     ([T, heads * dv] float32, rows may be strided).  ``seg_info`` [segments, 4] = slot, first row, length, first
-    position; None: every row is a portion of one token.  Returns [T, heads * dv] in ``out_dtype``."""
-    _cuda(proj, conv_w, dt_bias, rate, out_weight, token_slot, seg_info, state)
+    position; None: every row is a portion of one token.  ``conv_t``: the taps once more as [taps, channels],
+    which lets the kernels take eight channels per access.  Returns [T, heads * dv] in ``out_dtype``."""
+    _cuda(proj, conv_w, dt_bias, rate, out_weight, token_slot, seg_info, state, conv_t)
     tokens, ld = proj.shape
     assert a.dtype == gate.dtype == dt_bias.dtype == rate.dtype == out_weight.dtype == state.dtype == torch.float32
     assert a.stride(1) == 1 and gate.stride(1) == 1 and conv_w.dtype == proj.dtype and state.dim() == 2
@@ -801,9 +802,10 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, a: torch.Ten
         t = ws[at:at + tokens * n]
         at += tokens * n
         return t
-    qn, kn, vv, decay, beta, o_raw = (take(kv_heads * dk), take(kv_heads * dk), take(heads * dv), take(heads * dk),
-                                      take(heads), take(heads * dv))
-    _check(lib().tllm_delta_prepare(_p(proj), ld, _dt(proj), _p(conv_w), taps, a.data_ptr(), a.stride(0), _p(dt_bias), _p(rate),
+    # q, k and the decays first: their rows start on 16-byte boundaries wherever dk is a multiple of four
+    qn, kn, decay, vv, o_raw, beta = (take(kv_heads * dk), take(kv_heads * dk), take(heads * dk), take(heads * dv),
+                                      take(heads * dv), take(heads))
+    _check(lib().tllm_delta_prepare(_p(proj), ld, _dt(proj), _p(conv_w), _p(conv_t), taps, a.data_ptr(), a.stride(0), _p(dt_bias), _p(rate),
                                     _p(token_slot), _p(state), state.stride(0), heads, kv_heads, dk, dv, float(q_scale),
                                     float(unit_eps), _p(qn), _p(kn), _p(vv), _p(decay), _p(beta), tokens, _stream()),
            "delta_prepare")

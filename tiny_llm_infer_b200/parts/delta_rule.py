@@ -86,8 +86,11 @@ class ChannelDeltaRule:
     def load(self, t: Dict[str, torch.Tensor]) -> None:
         q, k, v, b, a_log, norm, a1, a2, dt_bias, g1, g2, o = self.names
         cs = self.conv_suffix
-        self.w_in = torch.cat([t[q], t[k], t[v], t[b]], dim=0).contiguous()
+        rows = self.channels + self.heads
+        pad = torch.zeros((-rows % 8, self.hidden), dtype=t[q].dtype, device=t[q].device)     # rows of the product's
+        self.w_in = torch.cat([t[q], t[k], t[v], t[b], pad], dim=0).contiguous()              # result on 16-byte steps
         self.conv_w = torch.cat([t[q + cs], t[k + cs], t[v + cs]], dim=0).to(self.w_in.dtype).contiguous()
+        self.conv_t = self.conv_w.t().contiguous()                                            # [taps, channels]
         self.w_low = torch.cat([t[a1], t[g1]], dim=0).contiguous()
         ra, rg = self.decay_rank, self.gate_rank
         second = torch.zeros((self.heads * (self.dk + self.dv), ra + rg), dtype=t[a2].dtype, device=t[a2].device)
@@ -122,5 +125,5 @@ class ChannelDeltaRule:
         split = self.heads * self.dk
         out = ops.delta_rule(proj, self.conv_w, self.taps, second[:, :split], self.dt_bias, self.rate, second[:, split:],
                              self.out_weight, self.norm_eps, ctx.token_slot, ctx.seg_info, cache.state, self.heads,
-                             self.kv_heads, self.dk, self.dv, self.dk ** -0.5, self.unit_eps, self.dtype)
+                             self.kv_heads, self.dk, self.dv, self.dk ** -0.5, self.unit_eps, self.dtype, conv_t=self.conv_t)
         return ops.linear(out, self.w_o, out_dtype=self.dtype)
