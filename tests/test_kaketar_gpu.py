@@ -137,6 +137,28 @@ def test_plain_feed_forward_and_token_side_input(dtype, rows):
     assert (got - want).abs().max() < tol * want.abs().max()
 
 
+@pytest.mark.parametrize("act", ["gelu_erf", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("rows", [3, 1024, 40])
+def test_products_with_a_plain_activation_in_their_epilogue(act, rows):
+    """The weight-streaming product (few rows) and the tcgen05 product (many) with the activation on every
+    output in the same kernel, against the float64 arithmetic of the same operands; in between the library's
+    product followed by the activation kernel."""
+    from tiny_llm_infer_b200 import ops
+    torch.manual_seed(rows)
+    k, n = 256, 8192
+    x = torch.randn(rows, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(torch.bfloat16)
+    before = ops.launches
+    got = ops.linear_act(x, w, act, torch.bfloat16)
+    fused = rows <= ops.SKINNY_MAX_ROWS or ops.tcgen05_pays(rows, n, k, torch.bfloat16)
+    assert fused == (rows != 40) and ops.launches - before == 1     # one kernel of this package either way: the fused
+                                                                    # product, or the activation behind the library's product
+    ops.check_error_word(x.device)
+    f = {"gelu_erf": plain.gelu_erf, "gelu_tanh": plain.gelu_tanh, "silu": plain.silu}[act]
+    want = f(x.double() @ w.double().t())
+    assert (got.double() - want).abs().max() < 0.02 * want.abs().max()
+
+
 # ----------------------------------------------------------------------------- attention over cached latents
 def latent_reference(q, kv, heads, dv, scale, window, sink):
     """q [T, H, dk], kv [T, dk] float64 (one shared key per token whose first dv elements are its value)."""

@@ -56,7 +56,7 @@ struct SkinnyStage {
 // inlined, the SwiGLU form costs the kernel ten registers more than the plain one (88 instead of
 // 78) and with them the third block per SM (the gate/up product of Qwen3-8B sizes: 42.5 us at two
 // blocks per SM, 35.1 at three, as the plain product of the same rows).
-template <int NT, typename TOut, bool SWIGLU, int ACT>
+template <int NT, typename TOut, bool SWIGLU, int ACT, bool UNARY>
 __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut* y, int M, int N, int r0) {
     constexpr int kRows = SWIGLU ? 8 : 16;                   // output columns of the block
     for (int idx = threadIdx.x; idx < kRows * NT * 8; idx += blockDim.x) {
@@ -70,6 +70,8 @@ __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut*
 #pragma unroll
                 for (int ww = 0; ww < kSkinnyWarps; ++ww) up += red[ww][row + 8][tok];
                 s = gate_act(s, ACT) * up;
+            } else if (UNARY) {                              // a plain product with an activation on every output
+                s = gate_act(s, ACT);
             }
             y[(size_t)tok * N + r0 + row] = from_f32<TOut>(s);
         }
@@ -81,7 +83,7 @@ __device__ __noinline__ void skinny_epilogue(float (*red)[16][NT * 8 + 1], TOut*
 // that belong to them as its lower half, so that a gate sum and its up sum meet in one thread's
 // accumulator; it writes silu(gate) * up: y is [M, N].  The grid, the bytes per block, the memory
 // pattern and the registers are those of the plain product of the 2 N rows.
-template <int NT, typename TOut, bool SWIGLU, int STAGES, int ACT>
+template <int NT, typename TOut, bool SWIGLU, int STAGES, int ACT, bool UNARY>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, int N, int K) {
     __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
@@ -167,10 +169,10 @@ skinny_gemm_kernel(const bf16* x, const bf16* __restrict__ w, TOut* y, int M, in
         red[warp][rq + 8][nt * 8 + c * 2 + 1] = acc[nt][3];
     }
     __syncthreads();
-    skinny_epilogue<NT, TOut, SWIGLU, ACT>(red, y, M, N, r0);
+    skinny_epilogue<NT, TOut, SWIGLU, ACT, UNARY>(red, y, M, N, r0);
 }
 
-template <int NT, typename TOut, bool SWIGLU, int STAGES = 3, int ACT = kActSilu>
+template <int NT, typename TOut, bool SWIGLU, int STAGES = 3, int ACT = kActSilu, bool UNARY = false>
 static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(SWIGLU ? (N + 7) / 8 : (N + 15) / 16);
@@ -182,7 +184,7 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU, STAGES, ACT>, (const bf16*)x, (const bf16*)w,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT, TOut, SWIGLU, STAGES, ACT, UNARY>, (const bf16*)x, (const bf16*)w,
                                        (TOut*)y, M, N, K);
     if (e != cudaSuccess) {
         set_error("gemm_skinny: %s", cudaGetErrorString(e));
@@ -246,4 +248,20 @@ extern "C" int tllm_gemm_skinny_swiglu(const void* x, const void* w, void* y, in
     }
     if (M <= 8) return launch_skinny<1, bf16, true>(x, w, y, M, N, K, stream);
     return launch_skinny<2, bf16, true>(x, w, y, M, N, K, stream);
+}
+
+// y[M, N] = act(x . w^T) for at most 8 rows, bfloat16 out: the plain product with silu, the tanh GELU or the
+// exact GELU on every output, in the same kernel.
+extern "C" int tllm_gemm_skinny_act(const void* x, const void* w, void* y, int M, int N, int K, int act,
+                                    cudaStream_t stream) {
+    TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh || act == kActGeluErf, "gemm_skinny_act: unknown activation %d", act);
+    TLLM_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_skinny_act: bad sizes");
+    TLLM_REQUIRE(M <= 8, "gemm_skinny_act: %d rows exceed 8", M);
+    TLLM_REQUIRE(K % 8 == 0, "gemm_skinny_act: K = %d is no multiple of 8", K);
+    TLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15u) == 0,
+                 "gemm_skinny_act: operands must be 16-byte aligned");
+    if (M == 0) return 0;
+    if (act == kActGeluErf) return launch_skinny<1, bf16, false, 3, kActGeluErf, true>(x, w, y, M, N, K, stream);
+    if (act == kActGeluTanh) return launch_skinny<1, bf16, false, 3, kActGeluTanh, true>(x, w, y, M, N, K, stream);
+    return launch_skinny<1, bf16, false, 3, kActSilu, true>(x, w, y, M, N, K, stream);
 }

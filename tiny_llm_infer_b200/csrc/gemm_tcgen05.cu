@@ -49,6 +49,16 @@ __device__ __forceinline__ float fast_gate_act(float g) {
     return __fdividef(g, 1.0f + __expf(-g));
 }
 
+// An activation on every output of a plain product (ACT: a GateAct code, or kActNone for none): silu and the
+// tanh GELU as above, the exact GELU 0.5 g (1 + erf(g / sqrt 2)) with the library's erff.
+constexpr int kActNone = -1;
+template <int ACT>
+__device__ __forceinline__ float unary_act(float g) {
+    if (ACT == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
+    if (ACT == kActNone) return g;
+    return fast_gate_act<ACT>(g);
+}
+
 __device__ __forceinline__ uint32_t cvta_shared(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -361,8 +371,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            v[i] = __uint_as_float(r0[i]);
-                            v[32 + i] = __uint_as_float(r1[i]);
+                            v[i] = unary_act<ACT>(__uint_as_float(r0[i]));
+                            v[32 + i] = unary_act<ACT>(__uint_as_float(r1[i]));
                         }
                     }
                     // through the warp's staging tile, so that a store instruction writes whole
@@ -445,7 +455,7 @@ static int sm_count() {
     return n;
 }
 
-template <bool SWIGLU, int MT, int ACT = kActSilu>
+template <bool SWIGLU, int MT, int ACT = (SWIGLU ? (int)kActSilu : kActNone)>
 static int launch_tcgen05(const CUtensorMap& mx, const CUtensorMap& mw, void* y, int M, int N, int K, int half_n,
                           int interleaved, int* error_word, cudaStream_t stream,
                           const GroupedTiles grouped = GroupedTiles{nullptr, nullptr, nullptr, nullptr, 0},
@@ -493,7 +503,17 @@ extern "C" int tllm_gemm_tcgen05(const void* x, const void* w, void* y, int M, i
     const bool tall = M > 128 && !(swiglu & 2) ;          // blocks of 256 rows once there are that many
     TLLM_REQUIRE(make_map(&mx, x, M, K, tall ? 2 * kBM : kBM) && make_map(&mw, w, N, K, 128),
                  "gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
-    const int act = swiglu >> 8;                            // bits 8 and up: the gate's activation (GateAct)
+    const int act = swiglu >> 8;                            // bits 8 and up: the activation (GateAct)
+    if (swiglu & 16) {                                      // a plain product with an activation on every output
+        TLLM_REQUIRE(!(swiglu & 1), "gemm_tcgen05: either a gated or a plain activation");
+#define UNARY(A) (tall ? launch_tcgen05<false, 2, A>(mx, mw, y, M, N, K, 0, 0, error_word, stream)                \
+                       : launch_tcgen05<false, 1, A>(mx, mw, y, M, N, K, 0, 0, error_word, stream))
+        if (act == kActGeluErf) return UNARY(kActGeluErf);
+        if (act == kActGeluTanh) return UNARY(kActGeluTanh);
+        if (act == kActSilu) return UNARY(kActSilu);
+#undef UNARY
+        TLLM_REQUIRE(false, "gemm_tcgen05: unknown activation %d", act);
+    }
     TLLM_REQUIRE(act == kActSilu || act == kActGeluTanh, "gemm_tcgen05: unknown activation %d", act);
     if ((swiglu & 1) && act == kActGeluTanh)
         return tall ? launch_tcgen05<true, 2, kActGeluTanh>(mx, mw, y, M, N, K, N / 2, interleaved, error_word, stream)

@@ -105,6 +105,7 @@ def _declare(h) -> None:
         "tllm_gemm_plain": [vp, i32, vp, i32, vp, i32, i32, i32, i32, vp],
         "tllm_gemm_tcgen05": [vp, vp, vp, i32, i32, i32, i32, vp, vp],
         "tllm_gemm_skinny_swiglu": [vp, vp, vp, i32, i32, i32, i32, vp],
+        "tllm_gemm_skinny_act": [vp, vp, vp, i32, i32, i32, i32, vp],
         "tllm_paged_attention_decode": [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32,
                                         i32, vp, vp, vp, vp],
         "tllm_paged_attention_prefill": [vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
@@ -528,7 +529,7 @@ def tcgen05_pays(rows: int, out_cols: int, k: int, dtype, col_tile: int = 256) -
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, short_tiles: bool = False,
-                 interleaved: bool = False, act: str = "silu") -> torch.Tensor:
+                 interleaved: bool = False, act: str = "silu", unary: bool = False) -> torch.Tensor:
     """y = x . weight^T on tcgen05 tensor cores fed by TMA (csrc/gemm_tcgen05.cu), bfloat16 in
     and out, float32 accumulation in tensor memory.  With ``swiglu`` the weight is [gate; up]
     (or, ``interleaved``, gate and up rows interleaved by eight) and the result is
@@ -543,7 +544,8 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, sh
         return y
     global tcgen05_calls
     tcgen05_calls += 1
-    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0) | (4 if interleaved else 0) | (ACTIVATIONS[act] << 8 if swiglu else 0),
+    _check(lib().tllm_gemm_tcgen05(_p(x), _p(weight), _p(y), rows, n, k, int(swiglu) | (2 if short_tiles else 0) | (4 if interleaved else 0) | (16 if unary else 0)
+                                   | (ELEMENTWISE_ACTIVATIONS[act] << 8 if (swiglu or unary) else 0),
                                    _p(error_word(x.device)), _stream()), "gemm_tcgen05")
     return y
 
@@ -745,6 +747,24 @@ def stream_add(h: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor
     _check(lib().tllm_stream_add(_p(h), _p(delta), _p(post_gain), gdt, float(post_eps), _p(out), _dt(out), h.shape[0],
                                  h.shape[1], _stream()), "stream_add")
     return out
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(x . weight^T) with ``act`` one of ``ELEMENTWISE_ACTIVATIONS``.  In bfloat16 the activation sits in the
+    product's epilogue where this package's own products run (at most 8 rows: the weight-streaming kernel; from
+    256 rows on, where the tiles fill the GPU: the tcgen05 kernel); else the product is followed by the
+    activation kernel."""
+    rows, k = x.shape
+    plain = x.dtype == weight.dtype == out_dtype == torch.bfloat16 and x.is_contiguous() and weight.is_contiguous()
+    if plain and 0 < rows <= SKINNY_MAX_ROWS and k % 8 == 0:
+        _cuda(x, weight)
+        out = torch.empty((rows, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+        _check(lib().tllm_gemm_skinny_act(_p(x), _p(weight), _p(out), rows, weight.shape[0], k,
+                                          ELEMENTWISE_ACTIVATIONS[act], _stream()), "gemm_skinny_act")
+        return out
+    if plain and tcgen05_pays(rows, weight.shape[0], k, weight.dtype):
+        return gemm_tcgen05(x, weight, act=act, unary=True)
+    return activation(linear(x, weight, out_dtype=out_dtype), act)
 
 
 def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:

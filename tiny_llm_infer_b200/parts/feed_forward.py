@@ -83,8 +83,7 @@ class PlainFeedForward:
         return 2 * tokens * self.inter
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        z = ops.linear(x, self.w_up, out_dtype=self.dtype)
-        return ops.linear(ops.activation(z, self.activation), self.w_down, out_dtype=self.dtype)
+        return ops.linear(ops.linear_act(x, self.w_up, self.activation, self.dtype), self.w_down, out_dtype=self.dtype)
 
 
 @register("feed_forward", "token_side")
