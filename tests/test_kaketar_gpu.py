@@ -517,6 +517,26 @@ def test_greedy_generation_equals_plain(name, budget, blocks, tmp_path):
     assert all(v == blocks for v in llm.cache.free_pages().values())
 
 
+def test_a_model_of_delta_rule_layers_alone(tmp_path):
+    """No layer with a cache: the cache manager has no group of pages at all and only the state slots."""
+    from tiny_llm_infer_b200 import LLM, SamplingParams
+    from tiny_kaketar import delta
+    from tiny_llm_infer_b200.config.kaketar import KaketarConfig
+    tiny = dict(cfg=KaketarConfig(vocab=150, width=64, max_positions=96, embedding_scale=1.5, norm_eps=1e-5, layers=(
+        delta(2, 1, 24, 16, 3, (8, 8), ff=80), delta(4, 4, 8, 8, 2, (8, 8))), logit_softcap=None, side_dim=4),
+        seed=31, std=0.1, norm_range=(0.7, 1.3))
+    folder = make_folder(tiny, tmp_path)
+    cfg, w = read_model(folder)
+    prompts = [prompt(i, n, cfg["vocab"]) for i, n in enumerate((19, 3, 40))]
+    want = [plain_greedy(cfg, w, p, 10) for p in prompts]
+    llm = LLM(str(folder), dtype="float32", max_model_len=96, num_kv_blocks=8, block_size=16,
+              max_num_batched_tokens=16, max_num_seqs=2)
+    assert not llm.cache.groups
+    outs = llm.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    assert [o.token_ids for o in outs] == want
+    llm.cache.audit()
+
+
 def test_long_decoding_in_bfloat16_through_graphs(tmp_path):
     """Sixty tokens each for three requests, decode steps replayed as CUDA graphs, bfloat16 kernels: every token
     is the plain implementation's choice given the same beginning, or within a near-tie of it."""
