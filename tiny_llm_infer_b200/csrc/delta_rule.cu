@@ -141,8 +141,14 @@ __global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restr
         else break;
     }
     const float* tail = state + (long long)slot * state_stride + tail_off;
-    for (int c = threadIdx.x * 8; c < channels; c += blockDim.x * 8) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    // With few rows a token's work is dealt to gridDim.y blocks: whole q and k heads (their norms need the
+    // head together), an even share of the v channels, of the decays, and the betas to the first.
+    const int Y = gridDim.y, yb = blockIdx.y;
+    const int u0 = (2 * kv_heads * yb) / Y, u1 = (2 * kv_heads * (yb + 1)) / Y;         // q heads, then k heads
+    const int vc = heads * dv / 8, v0 = 2 * qk + (vc * yb / Y) * 8, v1 = 2 * qk + (vc * (yb + 1) / Y) * 8;
+    auto conv8 = [&](int c, float (&acc)[8]) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
         for (int j = 0; j < taps; ++j) {
             float w[8], x[8];
             Ld8<T>::load(conv_t + (size_t)(taps - 1 - j) * channels + c, w);
@@ -153,10 +159,19 @@ __global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restr
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
-        if (c < 2 * qk) Ld8<float>::store(y + c, acc);
-        else Ld8<float>::store(vv + (size_t)t * heads * dv + (c - 2 * qk), acc);
+    };
+    for (int c = u0 * dk + threadIdx.x * 8; c < u1 * dk; c += blockDim.x * 8) {
+        float acc[8];
+        conv8(c, acc);
+        Ld8<float>::store(y + (c - u0 * dk), acc);
     }
-    for (int e = threadIdx.x * 4; e < heads * dk; e += blockDim.x * 4) {
+    for (int c = v0 + threadIdx.x * 8; c < v1; c += blockDim.x * 8) {
+        float acc[8];
+        conv8(c, acc);
+        Ld8<float>::store(vv + (size_t)t * heads * dv + (c - 2 * qk), acc);
+    }
+    const int dq = heads * dk / 4, e0 = (dq * yb / Y) * 4, e1 = (dq * (yb + 1) / Y) * 4;
+    for (int e = e0 + threadIdx.x * 4; e < e1; e += blockDim.x * 4) {
         const float4 x = *reinterpret_cast<const float4*>(a + (size_t)t * lda + e);
         const float4 b = *reinterpret_cast<const float4*>(dt_bias + e);
         const float rt = rate[e / dk];
@@ -165,14 +180,15 @@ __global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restr
         g.z = expf(-rt * softplus_f32(x.z + b.z)); g.w = expf(-rt * softplus_f32(x.w + b.w));
         *reinterpret_cast<float4*>(decay + (size_t)t * heads * dk + e) = g;
     }
-    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-        const float b = to_f32<T>(proj[(size_t)t * ld + channels + h]);
-        beta[(size_t)t * heads + h] = 1.0f / (1.0f + expf(-b));
-    }
+    if (yb == 0)
+        for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+            const float b = to_f32<T>(proj[(size_t)t * ld + channels + h]);
+            beta[(size_t)t * heads + h] = 1.0f / (1.0f + expf(-b));
+        }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int u = warp; u < 2 * kv_heads; u += warps) {          // q heads, then k heads
-        const float* src = y + (size_t)u * dk;
+    for (int u = u0 + warp; u < u1; u += warps) {
+        const float* src = y + (size_t)(u - u0) * dk;
         float sum = 0.0f;
         for (int e = lane * 4; e < dk; e += 128) {
             const float4 v = *reinterpret_cast<const float4*>(src + e);
@@ -438,7 +454,8 @@ __global__ void delta_finish_vec_kernel(const float* o_raw, const float* gate, i
         for (int e = threadIdx.x; e < heads * dv; e += blockDim.x) out[(size_t)t * heads * dv + e] = from_f32<T>(0.0f);
         return;
     }
-    for (int h = warp; h < heads; h += warps) {
+    const int Y = gridDim.y, yb = blockIdx.y;          // with few rows a token's heads and channels are dealt to gridDim.y blocks
+    for (int h = heads * yb / Y + warp; h < heads * (yb + 1) / Y; h += warps) {
         const float* src = o_raw + ((size_t)t * heads + h) * dv;
         float sum = 0.0f;
         for (int e = lane * 4; e < dv; e += 128) {
@@ -463,7 +480,8 @@ __global__ void delta_finish_vec_kernel(const float* o_raw, const float* gate, i
         while (len < taps - 1 && t - len >= 0 && token_slot[t - len] == slot) ++len;
         float* tail = state + (long long)slot * state_stride + tail_off;
         const int keep = taps - 1;
-        for (int c = threadIdx.x * 8; c < channels; c += blockDim.x * 8) {
+        const int cc = channels / 8;
+        for (int c = (cc * yb / Y) * 8 + threadIdx.x * 8; c < (cc * (yb + 1) / Y) * 8; c += blockDim.x * 8) {
             for (int i = 0; i < keep; ++i) {         // ascending: an old entry is read before its place is written
                 const int from_end = keep - i;
                 float x[8];
@@ -508,7 +526,11 @@ int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, 
     const bool vec = conv_t != nullptr && dk % 8 == 0 && dv % 8 == 0 && ld % 8 == 0 && lda % 4 == 0 && tail_off % 4 == 0 &&
                      state_stride % 4 == 0 && al(proj) && al(conv_t) && al(a) && al(dt_bias) && al(state) && al(qn) && al(kn) &&
                      al(vv) && al(decay);
-    const size_t smem = (size_t)(vec ? 2 * kv_heads * dk : channels) * sizeof(float);
+    // blocks per token: one where the rows fill the GPU, else up to a q or k head each
+    const int sms_p = sm_count_cached() > 0 ? sm_count_cached() : 148;
+    int split = 1;
+    if (vec) while (split * 2 <= 2 * kv_heads && (long long)n_rows * split < 2LL * sms_p) split *= 2;
+    const size_t smem = (size_t)(vec ? (2 * kv_heads + split - 1) / split * dk + dk : channels) * sizeof(float);
     TLLM_REQUIRE(smem <= 200 * 1024, "delta_prepare: %d channels do not fit in shared memory", channels);
 #define PREP(T)                                                                                                  \
     do {                                                                                                         \
@@ -517,7 +539,7 @@ int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, 
                 cudaError_t e = cudaFuncSetAttribute(delta_prepare_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
                 if (e != cudaSuccess) { set_error("delta_prepare: %s", cudaGetErrorString(e)); return (int)e; }  \
             }                                                                                                    \
-            launch_pdl(kPdlOther, delta_prepare_vec_kernel<T>, dim3(n_rows), dim3(256), smem, stream, (const T*)proj, ld, \
+            launch_pdl(kPdlOther, delta_prepare_vec_kernel<T>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), smem, stream, (const T*)proj, ld, \
                        (const T*)conv_t, taps, a, lda, dt_bias, rate, token_slot, state, state_stride, tail_off, \
                        heads, kv_heads, dk, dv, q_scale, unit_eps, qn, kn, vv, decay, beta, n_rows);             \
             break;                                                                                               \
@@ -596,10 +618,13 @@ int tllm_delta_finish(const float* o_raw, const float* gate, int ldg, const floa
     const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vec = dv % 4 == 0 && ldg % 4 == 0 && channels % 8 == 0 && ld % 8 == 0 && tail_off % 4 == 0 && state_stride % 4 == 0 &&
                      al(o_raw) && al(gate) && al(weight) && al(proj) && al(state);
+    const int sms_f = sm_count_cached() > 0 ? sm_count_cached() : 148;
+    int split = 1;
+    while (vec && split * 2 <= heads && (long long)n_rows * split < 2LL * sms_f) split *= 2;
 #define FIN(T)                                                                                                             \
     do {                                                                                                                   \
         if (vec)                                                                                                           \
-            launch_pdl(kPdlOther, delta_finish_vec_kernel<T>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps, \
+            launch_pdl(kPdlOther, delta_finish_vec_kernel<T>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), 0, stream, o_raw, gate, ldg, weight, eps, \
                        token_slot, n_rows, heads, dv, (T*)out, (const T*)proj, ld, channels, taps, state, state_stride, tail_off); \
         else                                                                                                               \
             launch_pdl(kPdlOther, delta_finish_kernel<T>, dim3(n_rows), dim3(256), 0, stream, o_raw, gate, ldg, weight, eps, \

@@ -81,7 +81,9 @@ __global__ void latent_query_kernel(const T* q, const T* lat, int heads, int pla
         return;
     }
     const int pos = positions[t];
-    for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+    const int total = heads * width, per_block = (total + gridDim.y - 1) / gridDim.y;     // few rows: a row over several blocks
+    const int i_end = min(total, (int)(blockIdx.y + 1) * per_block);
+    for (int i = blockIdx.y * per_block + threadIdx.x; i < i_end; i += blockDim.x) {
         const int h = i / width, e = i - h * width;
         T* dst = out + ((size_t)t * heads + h) * width;
         if (e < rank) {
@@ -106,7 +108,9 @@ __global__ void heads_gate_kernel(const T* x, const T* gate, int ldg, int heads,
     TLLM_PDL_ENTER();
     const int t = blockIdx.x;
     const bool pad = token_slot != nullptr && token_slot[t] < 0;
-    for (int i = threadIdx.x; i < heads * width; i += blockDim.x) {
+    const int total = heads * width, per_block = (total + gridDim.y - 1) / gridDim.y;
+    const int i_end = min(total, (int)(blockIdx.y + 1) * per_block);
+    for (int i = blockIdx.y * per_block + threadIdx.x; i < i_end; i += blockDim.x) {
         const int h = i / width, e = i - h * width;
         float v = 0.0f;
         if (!pad) {
@@ -115,6 +119,14 @@ __global__ void heads_gate_kernel(const T* x, const T* gate, int ldg, int heads,
         }
         out[(size_t)t * heads * width + i] = from_f32<T>(v);
     }
+}
+
+// Blocks that share a row of `elements` when the rows alone would leave the GPU idle: at least 256 elements each.
+static int row_split(int rows, int elements) {
+    const int sms = sm_count_cached() > 0 ? sm_count_cached() : 148;
+    int split = 1;
+    while (split < 64 && (long long)rows * split < 2LL * sms && elements / (split * 2) >= 256) split *= 2;
+    return split;
 }
 
 }  // namespace tllm
@@ -151,11 +163,12 @@ int tllm_latent_query(const void* q, const void* lat, int dtype, int heads, int 
     TLLM_REQUIRE(tokens >= 0 && heads > 0 && plain >= 0 && rot >= 0 && rank > 0 && rot_dims <= rot && rot_dims % 2 == 0,
                  "latent_query: bad sizes");
     if (tokens == 0) return 0;
+    const int split = row_split(tokens, heads * (rank + rot));
     if (dtype == kBF16)
-        launch_pdl(kPdlQk, latent_query_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)q, (const bf16*)lat, heads,
+        launch_pdl(kPdlQk, latent_query_kernel<bf16>, dim3(tokens, split), dim3(256), 0, stream, (const bf16*)q, (const bf16*)lat, heads,
                    plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (bf16*)out);
     else if (dtype == kF32)
-        launch_pdl(kPdlQk, latent_query_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)q, (const float*)lat, heads,
+        launch_pdl(kPdlQk, latent_query_kernel<float>, dim3(tokens, split), dim3(256), 0, stream, (const float*)q, (const float*)lat, heads,
                    plain, rot, rot_dims, rank, freq, mag, positions, token_slot, tokens, (float*)out);
     else TLLM_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
     return finish_launch("latent_query");
@@ -165,11 +178,12 @@ int tllm_heads_gate(const void* x, const void* gate, int ldg, int dtype, int hea
                     const int* token_slot, void* out, cudaStream_t stream) {
     TLLM_REQUIRE(tokens >= 0 && heads > 0 && width > 0 && (gate == nullptr || ldg >= heads * width), "heads_gate: bad sizes");
     if (tokens == 0) return 0;
+    const int split = row_split(tokens, heads * width);
     if (dtype == kBF16)
-        launch_pdl(kPdlOther, heads_gate_kernel<bf16>, dim3(tokens), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, ldg,
+        launch_pdl(kPdlOther, heads_gate_kernel<bf16>, dim3(tokens, split), dim3(256), 0, stream, (const bf16*)x, (const bf16*)gate, ldg,
                    heads, width, tokens, token_slot, (bf16*)out);
     else if (dtype == kF32)
-        launch_pdl(kPdlOther, heads_gate_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)x, (const float*)gate, ldg,
+        launch_pdl(kPdlOther, heads_gate_kernel<float>, dim3(tokens, split), dim3(256), 0, stream, (const float*)x, (const float*)gate, ldg,
                    heads, width, tokens, token_slot, (float*)out);
     else TLLM_REQUIRE(false, "heads_gate: unknown dtype %d", dtype);
     return finish_launch("heads_gate");
