@@ -54,7 +54,15 @@ K3 = dict(cfg=KaketarConfig(vocab=512, width=160, max_positions=400, embedding_s
     delta(5, 5, 16, 16, 5, (24, 8)),
 ), logit_softcap=30.0, side_dim=24), seed=23, std=0.07, norm_range=(0.8, 1.2), page_size=32,
     lengths=(70, 300, 130, 41, 210, 35))
-KAKETARS = {"K1": K1, "K2": K2, "K3": K3}
+# nothing a multiple of eight, little a multiple of four: width 100, key widths 10 and 6, value widths 6 and 10,
+# six taps, a window of 3, a rotation of 2 of 6 rotated elements, five and three heads, a side input of 3
+K4 = dict(cfg=KaketarConfig(vocab=333, width=100, max_positions=200, embedding_scale=0.5, norm_eps=2e-5, layers=(
+    latent(5, 6, 6, 10, 12, 10, 0.4, 77.0, 2, 3, (3.0, 20.0, 6.0, 1.5), ff=50),
+    delta(3, 1, 10, 6, 6, (8, 9)),
+    delta(2, 2, 6, 10, 1, (11, 8), ff=30),
+), logit_softcap=5.0, side_dim=3), seed=24, std=0.12, norm_range=(0.7, 1.3), page_size=16,
+    lengths=(70, 97, 41, 35, 66))
+KAKETARS = {"K1": K1, "K2": K2, "K3": K3, "K4": K4}
 
 
 def make_folder(tiny, folder=None, dtype=torch.bfloat16) -> Path:
