@@ -122,7 +122,9 @@ template <> struct Ld8<bf16> {
 
 // The same with eight channels per thread and access (rows of proj, the taps as [taps][channels], dk and dv
 // multiples of eight, everything on 16-byte boundaries).
-template <typename T>
+// TAPS: the number of taps if it is 2, 3 or 4 (their loads are then all issued before the first product), 0 for
+// any other number.
+template <typename T, int TAPS>
 __global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restrict__ conv_t, int taps,
                                          const float* a, int lda, const float* __restrict__ dt_bias,
                                          const float* __restrict__ rate, const int* __restrict__ token_slot,
@@ -149,13 +151,27 @@ __global__ void delta_prepare_vec_kernel(const T* proj, int ld, const T* __restr
     auto conv8 = [&](int c, float (&acc)[8]) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-        for (int j = 0; j < taps; ++j) {
-            float w[8], x[8];
-            Ld8<T>::load(conv_t + (size_t)(taps - 1 - j) * channels + c, w);
-            if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + c, x);
-            else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+        if (TAPS > 0) {
+            float w[TAPS > 0 ? TAPS : 1][8], x[TAPS > 0 ? TAPS : 1][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+            for (int j = 0; j < TAPS; ++j) {
+                Ld8<T>::load(conv_t + (size_t)(TAPS - 1 - j) * channels + c, w[j]);
+                if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + c, x[j]);
+                else Ld8<float>::load(tail + (size_t)(TAPS - 1 - (j - back)) * channels + c, x[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] += w[j][e] * x[j][e];
+        } else {
+            for (int j = 0; j < taps; ++j) {
+                float w[8], x[8];
+                Ld8<T>::load(conv_t + (size_t)(taps - 1 - j) * channels + c, w);
+                if (j <= back) Ld8<T>::load(proj + (size_t)(t - j) * ld + c, x);
+                else Ld8<float>::load(tail + (size_t)(taps - 1 - (j - back)) * channels + c, x);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] += w[e] * x[e];
+            }
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
@@ -532,16 +548,23 @@ int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, 
     if (vec) while (split * 2 <= 2 * kv_heads && (long long)n_rows * split < 2LL * sms_p) split *= 2;
     const size_t smem = (size_t)(vec ? (2 * kv_heads + split - 1) / split * dk + dk : channels) * sizeof(float);
     TLLM_REQUIRE(smem <= 200 * 1024, "delta_prepare: %d channels do not fit in shared memory", channels);
+#define PREP_VEC(T, N)                                                                                           \
+    do {                                                                                                         \
+        if (smem > 48 * 1024) {                                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(delta_prepare_vec_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) { set_error("delta_prepare: %s", cudaGetErrorString(e)); return (int)e; }      \
+        }                                                                                                        \
+        launch_pdl(kPdlOther, delta_prepare_vec_kernel<T, N>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), smem, stream, \
+                   (const T*)proj, ld, (const T*)conv_t, taps, a, lda, dt_bias, rate, token_slot, state, state_stride,   \
+                   tail_off, heads, kv_heads, dk, dv, q_scale, unit_eps, qn, kn, vv, decay, beta, n_rows);       \
+    } while (0)
 #define PREP(T)                                                                                                  \
     do {                                                                                                         \
         if (vec) {                                                                                               \
-            if (smem > 48 * 1024) {                                                                              \
-                cudaError_t e = cudaFuncSetAttribute(delta_prepare_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-                if (e != cudaSuccess) { set_error("delta_prepare: %s", cudaGetErrorString(e)); return (int)e; }  \
-            }                                                                                                    \
-            launch_pdl(kPdlOther, delta_prepare_vec_kernel<T>, dim3(n_rows, split), dim3(split > 1 ? 128 : 256), smem, stream, (const T*)proj, ld, \
-                       (const T*)conv_t, taps, a, lda, dt_bias, rate, token_slot, state, state_stride, tail_off, \
-                       heads, kv_heads, dk, dv, q_scale, unit_eps, qn, kn, vv, decay, beta, n_rows);             \
+            if (taps == 2) PREP_VEC(T, 2);                                                                       \
+            else if (taps == 3) PREP_VEC(T, 3);                                                                  \
+            else if (taps == 4) PREP_VEC(T, 4);                                                                  \
+            else PREP_VEC(T, 0);                                                                                 \
             break;                                                                                               \
         }                                                                                                        \
         if (smem > 48 * 1024) {                                                                                  \
@@ -556,6 +579,7 @@ int tllm_delta_prepare(const void* proj, int ld, int dtype, const void* conv_w, 
     else if (dtype == kF32) PREP(float);
     else TLLM_REQUIRE(false, "delta_prepare: unknown dtype %d", dtype);
 #undef PREP
+#undef PREP_VEC
     return finish_launch("delta_prepare");
 }
 
